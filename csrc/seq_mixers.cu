@@ -65,35 +65,40 @@ embed_sinusoid_kernel(const int* __restrict__ ids, const int* __restrict__ pos, 
 }
 
 // ------------------------------------------------------------------------------------------------ residual + norms
-// One CTA per row.  y (optional): residual += y / rms(y) * w_post.  extra (optional): residual += extra.
-// w_pre (optional): out = residual / rms(residual) * w_pre.
+// One CTA per row.  y (optional): residual += mult * y / rms(y) * w_post, or += mult * y without w_post.  extra
+// (optional): residual += extra.  w_pre (optional): out = residual / rms(residual) * w_pre; out without w_pre: the
+// residual itself in the activation type.
 template <typename T>
 __global__ void __launch_bounds__(256)
 resid_norm_step_kernel(float* __restrict__ resid, const T* __restrict__ y, const T* __restrict__ w_post,
                        const float* __restrict__ extra, const T* __restrict__ w_pre, T* __restrict__ out, int width,
-                       float eps) {
+                       float eps, float mult) {
   __shared__ float red[32];
   const long long base = (long long)blockIdx.x * width;
   float* r = resid + base;
-  float inv_y = 0.f;
-  if (y != nullptr) {
+  float inv_y = mult;
+  if (y != nullptr && w_post != nullptr) {
     float ss = 0.f;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
       const float v = to_f32<T>(y[base + c]);
       ss += v * v;
     }
     ss = block_sum(ss, red);
-    inv_y = 1.f / sqrtf(ss / (float)width + eps);
+    inv_y = mult / sqrtf(ss / (float)width + eps);
   }
   float ss2 = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float v = r[c];
-    if (y != nullptr) v += to_f32<T>(y[base + c]) * inv_y * to_f32<T>(w_post[c]);
+    if (y != nullptr) v += to_f32<T>(y[base + c]) * inv_y * (w_post ? to_f32<T>(w_post[c]) : 1.f);
     if (extra != nullptr) v += extra[base + c];
     if (y != nullptr || extra != nullptr) r[c] = v;
     ss2 += v * v;
   }
-  if (w_pre == nullptr) return;
+  if (out == nullptr) return;
+  if (w_pre == nullptr) {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) out[base + c] = from_f32<T>(r[c]);
+    return;
+  }
   ss2 = block_sum(ss2, red);
   const float inv = 1.f / sqrtf(ss2 / (float)width + eps);
   for (int c = threadIdx.x; c < width; c += blockDim.x)
@@ -138,6 +143,77 @@ qk_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* __restri
   }
 }
 
+// The same append for projections that pass a short causal filter first.  One CTA per token, one warp per head slot;
+// a lane holds channels lane + 32 i of its head (head sizes up to 256).  Every channel of q | k | v is filtered over time
+// (w [C, taps], last tap = current token; earlier inputs from this batch's rows, else from the slot's carried inputs
+// state [slots, taps-1, C], else zero; w null: no filter), q and k heads are divided by their root mean square and
+// multiplied by a weight of d entries that all heads share (null: none), and q by 1 + coef * ln(floor((pos + 1) / every)
+// + 1).  Filter sums, norms and the temperature are fp32.
+template <typename T>
+__global__ void __launch_bounds__(128)
+qkv_filter_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ w,
+                              const T* __restrict__ state, const int* __restrict__ seq_info,
+                              const T* __restrict__ q_w, const T* __restrict__ k_w, float* __restrict__ q_out,
+                              T* __restrict__ kcache, T* __restrict__ vcache, const int* __restrict__ tok_seq,
+                              const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks,
+                              int block_size, int Hq, int G, int d, int dv, int taps, float eps, int normalize,
+                              float temp_coef, int temp_every) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int pos = tok_pos[t];
+  const int* si = seq_info + 4 * tok_seq[t];
+  const int local = t - si[0], seen = si[2];
+  const int C = (Hq + G) * d + G * dv;
+  const T* st = state ? state + (long long)si[3] * (taps - 1) * C : nullptr;
+  const long long page = tables[(long long)tok_seq[t] * max_blocks + pos / block_size];
+  const long long slot = page * block_size + pos % block_size;
+  const float temp = temp_coef != 0.f ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every + 1)) : 1.f;
+  for (int s = warp; s < Hq + 2 * G; s += nw) {
+    const bool is_v = s >= Hq + G;
+    const int n = is_v ? dv : d;
+    const int col = is_v ? (Hq + G) * d + (s - Hq - G) * dv : s * d;
+    float v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;
+      v[i] = 0.f;
+      if (c >= n) continue;
+      const int ch = col + c;
+      if (w == nullptr) {
+        v[i] = to_f32<T>(qkv[(long long)t * ld + ch]);
+      } else {
+        float a = 0.f;
+        for (int j = 0; j < taps; ++j) {
+          const int src = local - j;
+          float u = 0.f;
+          if (src >= 0) u = to_f32<T>(qkv[(long long)(t - j) * ld + ch]);
+          else if (seen + src >= 0) u = to_f32<T>(st[(long long)(taps - 1 + src) * C + ch]);
+          a += to_f32<T>(w[(long long)ch * taps + (taps - 1 - j)]) * u;
+        }
+        v[i] = a;
+      }
+      ss += v[i] * v[i];
+    }
+    float inv = 1.f;
+    const T* hw = nullptr;
+    if (!is_v) {
+      ss = warp_sum(ss);
+      if (normalize) inv = 1.f / sqrtf(ss / (float)d + eps);
+      hw = s < Hq ? q_w : k_w;
+      if (s < Hq) inv *= temp;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;
+      if (c >= n) continue;
+      const float o = v[i] * inv * (hw ? to_f32<T>(hw[c]) : 1.f);
+      if (s < Hq) q_out[((long long)t * Hq + s) * d + c] = o;
+      else if (!is_v) kcache[(slot * G + (s - Hq)) * d + c] = from_f32<T>(o);
+      else vcache[(slot * G + (s - Hq - G)) * dv + c] = from_f32<T>(o);
+    }
+  }
+}
+
 // First position a query at `pos` attends to: the start of its aligned chunk (chunk > 0), else the start of a sliding
 // window of `window` positions that ends at the query (window > 0), else the start of the sequence.
 __device__ __forceinline__ int first_key(int pos, int chunk, int window) {
@@ -173,7 +249,9 @@ __global__ void __launch_bounds__(256, NV <= 2 ? 2 : 1)
 sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                            const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ atoms,
                            const int* __restrict__ tables, int max_blocks, int block_size, int Hq, int G, int d,
-                           int dv, float scale, int chunk, int window, int kpitch, int vpitch) {
+                           int dv, float scale, int chunk, int window, int kpitch, int vpitch,
+                           const float* __restrict__ dist_bias, int bias_len, const T* __restrict__ gate,
+                           long long gate_ld) {
   extern __shared__ __align__(16) float smf[];
   const int dp = d + 4, vp = NV * 64, pp = kBK + 4;
   float* Qs = smf;
@@ -264,6 +342,7 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
       for (int j = 0; j < 4; ++j) {
         const int kj = k0 + tx + 16 * j;
         if (!(r < nq && kj <= qp && kj >= lo)) s[i][j] = -INFINITY;
+        else if (dist_bias != nullptr) s[i][j] += __ldg(dist_bias + (long long)h * bias_len + min(qp - kj, bias_len - 1));
         mt = fmaxf(mt, s[i][j]);
       }
 #pragma unroll
@@ -316,7 +395,11 @@ sink_attention_tile_kernel(const float* __restrict__ q, const T* __restrict__ kc
       for (int e = 0; e < 4; ++e) {
         const int c = n * 64 + tx * 4 + e;
         const float2 a2 = acc[i][n * 2 + (e >> 1)];
-        if (c < dv) out[((long long)(row0 + r) * Hq + h) * dv + c] = from_f32<T>(((e & 1) ? a2.y : a2.x) * inv);
+        if (c < dv) {
+          float o = ((e & 1) ? a2.y : a2.x) * inv;
+          if (gate != nullptr) o *= sigmoid_f(to_f32<T>(gate[(long long)(row0 + r) * gate_ld + h * dv + c]));
+          out[((long long)(row0 + r) * Hq + h) * dv + c] = from_f32<T>(o);
+        }
       }
   }
 }
@@ -355,7 +438,8 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
                       const float* __restrict__ sink, T* __restrict__ out, const int* __restrict__ tok_seq,
                       const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks, int block_size,
                       int Hq, int G, int d, int dv, float scale, int chunk, int window, int kpitch, int vpitch,
-                      const int* __restrict__ atoms) {
+                      const int* __restrict__ atoms, const float* __restrict__ dist_bias, int bias_len,
+                      const T* __restrict__ gate, long long gate_ld) {
   // q [REP][d8] | partial values [kAW][REP][dv] | partial max [kAW][REP] | partial sum [kAW][REP] | key staging
   extern __shared__ __align__(16) float qs[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -439,7 +523,9 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
     float p[REP];
 #pragma unroll
     for (int hh = 0; hh < REP; ++hh) {
-      const float s = j <= pos ? sc[hh] : -INFINITY;
+      float s = j <= pos ? sc[hh] : -INFINITY;
+      if (dist_bias != nullptr && j <= pos)
+        s += __ldg(dist_bias + (long long)(h0 + hh) * bias_len + min(pos - j, bias_len - 1));
       const float mn = fmaxf(m[hh], warp_max(s));      // finite: the tile holds at least key j0
       const float corr = expf(m[hh] - mn);             // 0 on the first tile (m = -inf)
       p[hh] = (j <= pos) ? expf(s - mn) : 0.f;
@@ -511,7 +597,9 @@ sink_attention_kernel(const float* __restrict__ q, const T* __restrict__ kcache,
       L += pl[w * REP + hh] * f;
       o += pacc[(w * REP + hh) * dv + c] * f;
     }
-    out[((long long)t * Hq + h0 + hh) * dv + c] = from_f32<T>(L > 0.f ? o / L : 0.f);
+    float r = L > 0.f ? o / L : 0.f;
+    if (gate != nullptr) r *= sigmoid_f(to_f32<T>(gate[(long long)t * gate_ld + (h0 + hh) * dv + c]));
+    out[((long long)t * Hq + h0 + hh) * dv + c] = from_f32<T>(r);
   }
 }
 
@@ -519,7 +607,8 @@ template <typename T, int REP, int VPL>
 static int launch_attention_rows_v(dim3 grid, const void* q, const void* kcache, const void* vcache, const void* sink,
                                    void* out, const void* tok_seq, const void* tok_pos, const void* tables,
                                    int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale,
-                                   int chunk, int window, int kpitch, int vpitch, const int* atoms, cudaStream_t s) {
+                                   int chunk, int window, int kpitch, int vpitch, const int* atoms, const void* dist_bias,
+                                   int bias_len, const void* gate, long long gate_ld, cudaStream_t s) {
   const size_t smem = (size_t)(REP * ((d + 7) & ~7) + kAW * REP * dv + 2 * kAW * REP + kAW * 32 * 68) * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(sink_attention_kernel<T, REP, VPL>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -528,7 +617,7 @@ static int launch_attention_rows_v(dim3 grid, const void* q, const void* kcache,
   sink_attention_kernel<T, REP, VPL><<<grid, 32 * kAW, smem, s>>>(
       (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, (const int*)tok_seq,
       (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, window, kpitch,
-      vpitch, atoms);
+      vpitch, atoms, (const float*)dist_bias, bias_len, (const T*)gate, gate_ld);
   return SXB_OK;
 }
 
@@ -536,21 +625,23 @@ template <typename T, int REP>
 static int launch_attention_rows(dim3 grid, const void* q, const void* kcache, const void* vcache, const void* sink,
                                  void* out, const void* tok_seq, const void* tok_pos, const void* tables,
                                  int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
-                                 int window, int kpitch, int vpitch, const int* atoms, cudaStream_t s) {
+                                 int window, int kpitch, int vpitch, const int* atoms, const void* dist_bias,
+                                 int bias_len, const void* gate, long long gate_ld, cudaStream_t s) {
   if (dv <= 128)
     return launch_attention_rows_v<T, REP, 4>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos, tables, max_blocks,
                                               block_size, Hq, G, d, dv, scale, chunk, window, kpitch, vpitch, atoms,
-                                              s);
+                                              dist_bias, bias_len, gate, gate_ld, s);
   return launch_attention_rows_v<T, REP, kMaxVPerLane>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos, tables,
                                                        max_blocks, block_size, Hq, G, d, dv, scale, chunk, window,
-                                                       kpitch, vpitch, atoms, s);
+                                                       kpitch, vpitch, atoms, dist_bias, bias_len, gate, gate_ld, s);
 }
 
 // Query heads per key/value head that one CTA takes together: the largest of 8, 4, 2, 1 that divides the group.
 static int attention_rows(int dtype, dim3 grid, const void* q, const void* kcache, const void* vcache,
                           const void* sink, void* out, const void* tok_seq, const void* tok_pos, const void* tables,
                           int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
-                          int window, int kpitch, int vpitch, const int* atoms, cudaStream_t s) {
+                          int window, int kpitch, int vpitch, const int* atoms, const void* dist_bias, int bias_len,
+                          const void* gate, long long gate_ld, cudaStream_t s) {
   const int group = Hq / G;
   int rc = SXB_OK;
   // (Taking fewer heads together when a decode batch leaves SMs idle was measured slower: every CTA walks all keys.)
@@ -558,7 +649,8 @@ static int attention_rows(int dtype, dim3 grid, const void* q, const void* kcach
 #define ROWS(REP)                                                                                                      \
   SEQMIX_DISPATCH(dtype, (rc = launch_attention_rows<T, REP>(grid, q, kcache, vcache, sink, out, tok_seq, tok_pos,      \
                                                               tables, max_blocks, block_size, Hq, G, d, dv, scale,      \
-                                                              chunk, window, kpitch, vpitch, atoms, s)))
+                                                              chunk, window, kpitch, vpitch, atoms, dist_bias,      \
+                                                              bias_len, gate, gate_ld, s)))
   if (rep == 8) ROWS(8);
   else if (rep == 4) ROWS(4);
   else if (rep == 2) ROWS(2);
@@ -1283,16 +1375,17 @@ SXB_API int sxb_embed_sinusoid(const void* ids, const void* pos, const void* tab
   return SXB_OK;
 }
 
-/* Per row of the fp32 residual [rows, width]: if y: residual += y / rms(y) * w_post; if extra (fp32): residual += extra;
- * if w_pre: out = residual / rms(residual) * w_pre.  y, w_post, w_pre, out are `dtype`; any of the three parts may be
- * absent (null). */
+/* Per row of the fp32 residual [rows, width]: if y: residual += mult * y / rms(y) * w_post (without w_post: += mult * y);
+ * if extra (fp32): residual += extra; if w_pre: out = residual / rms(residual) * w_pre (out without w_pre: the residual in
+ * `dtype`).  y, w_post, w_pre, out are `dtype`; any of the parts may be absent (null). */
 SXB_API int sxb_resid_norm_step(void* resid, const void* y, const void* w_post, const void* extra, const void* w_pre,
-                                void* out, long long rows, int width, float eps, int dtype, void* stream) {
+                                void* out, long long rows, int width, float eps, float mult, int dtype,
+                                void* stream) {
   if (rows <= 0) return SXB_OK;
-  if ((y == nullptr) != (w_post == nullptr) || (w_pre == nullptr) != (out == nullptr)) return SXB_ERR_BAD_ARG;
+  if ((y == nullptr && w_post != nullptr) || (w_pre != nullptr && out == nullptr)) return SXB_ERR_BAD_ARG;
   SEQMIX_DISPATCH(dtype, (resid_norm_step_kernel<T><<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
                              (float*)resid, (const T*)y, (const T*)w_post, (const float*)extra, (const T*)w_pre,
-                             (T*)out, width, eps)));
+                             (T*)out, width, eps, mult)));
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }
@@ -1313,40 +1406,107 @@ SXB_API int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, 
   return SXB_OK;
 }
 
+/* As sxb_qk_norm_append for projections that pass a short causal filter over time first (conv_w `dtype` [C, taps] with
+ * C = Hq*d + G*d + G*dv, last tap = current token, or null; carried inputs state `dtype` [slots, taps-1, C], to be moved
+ * on with sxb_conv_state_update afterwards), with a norm weight of d entries shared by the heads (q_w / k_w, `dtype`, or
+ * null) and a query temperature 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1). */
+SXB_API int sxb_qkv_filter_norm_append(const void* qkv, long long ld, const void* conv_w, const void* state,
+                                       const void* seq_info, const void* q_w, const void* k_w, void* q_out,
+                                       void* kcache, void* vcache, const void* tok_seq, const void* tok_pos,
+                                       const void* tables, int n_tokens, int max_blocks, int block_size, int Hq, int G,
+                                       int d, int dv, int taps, float eps, int normalize, float temp_coef,
+                                       int temp_every, int dtype, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  if (d > 256 || dv > 256 || taps < 1 || taps > kMaxTaps || temp_every < 1) return SXB_ERR_UNSUPPORTED;
+  if (conv_w != nullptr && taps > 1 && state == nullptr) return SXB_ERR_BAD_ARG;
+  SEQMIX_DISPATCH(dtype, (qkv_filter_norm_append_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(
+                             (const T*)qkv, ld, (const T*)conv_w, (const T*)state, (const int*)seq_info, (const T*)q_w,
+                             (const T*)k_w, (float*)q_out, (T*)kcache, (T*)vcache, (const int*)tok_seq,
+                             (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, taps, eps,
+                             normalize, temp_coef, temp_every)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
 /* Attention of every token over the cached keys lo..pos of its sequence, scores and weights in fp32.  lo = start of the
  * token's chunk of `chunk` positions (chunk > 0), else pos - window + 1 clamped at 0 (window > 0), else 0.  sink (fp32
  * [Hq] or null) adds exp(sink[h]) to the denominator.  Key rows sit at kcache + slot * k_pitch + g * d and value rows at
  * vcache + slot * v_pitch + g * dv (pitches in elements; 0 = packed [pages, block_size, G, d|dv]), so values may be a
- * column range of the key rows.  out `dtype` [n_tokens, Hq * dv] (the caches have the same type).  One CTA per
- * (token, head group). */
+ * column range of the key rows.  out `dtype` [n_tokens, Hq * dv] (the caches have the same type).  dist_bias (fp32
+ * [Hq, bias_len] or null) is added to the scaled score of a key at distance n = query position - key position:
+ * dist_bias[h, min(n, bias_len - 1)].  gate (`dtype` rows of pitch gate_ld with Hq * dv channels, or null): the output is
+ * multiplied by sigmoid(gate).  One CTA per (token, head group). */
 SXB_API int sxb_sink_attention(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens,
                                int max_blocks, int block_size, int Hq, int G, int d, int dv, float scale, int chunk,
-                               int window, int k_pitch, int v_pitch, int dtype, void* stream) {
+                               int window, int k_pitch, int v_pitch, const void* dist_bias, int bias_len,
+                               const void* gate, long long gate_ld, int dtype, void* stream) {
   if (n_tokens <= 0) return SXB_OK;
-  if (dv > 32 * kMaxVPerLane || Hq % G) return SXB_ERR_UNSUPPORTED;
+  if (dv > 32 * kMaxVPerLane || Hq % G || (dist_bias != nullptr && bias_len < 1)) return SXB_ERR_UNSUPPORTED;
   if (k_pitch <= 0) k_pitch = G * d;
   if (v_pitch <= 0) v_pitch = G * dv;
   const int rc = attention_rows(dtype, dim3(n_tokens, 1), q, kcache, vcache, sink, out, tok_seq, tok_pos, tables,
                                 max_blocks, block_size, Hq, G, d, dv, scale, chunk, window, k_pitch, v_pitch, nullptr,
-                                (cudaStream_t)stream);
+                                dist_bias, bias_len, gate, gate_ld, (cudaStream_t)stream);
   if (rc != SXB_OK) return rc;
   SXB_CHECK_LAUNCH();
   return SXB_OK;
+}
+
+
+// ------------------------------------------------------------------------------------------------ token side input
+// g[t, c] = gelu_tanh(gx[t, c]) * table[ids[t], col0 + c] for c < dim, 0 for dim <= c < out_w.
+template <typename T>
+__global__ void __launch_bounds__(256)
+side_gate_kernel(const T* __restrict__ gx, long long ld, const T* __restrict__ table, long long table_ld,
+                 const int* __restrict__ ids, T* __restrict__ out, long long total, int dim, int out_w, int col0) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / out_w;
+  const int c = (int)(i % out_w);
+  float g = 0.f;
+  if (c < dim) {
+    const float z = to_f32<T>(gx[t * ld + c]);
+    const float a = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    g = a * to_f32<T>(table[(long long)ids[t] * table_ld + col0 + c]);
+  }
+  out[i] = from_f32<T>(g);
+}
+
+// x <- cap * tanh(x * scale / cap) (cap > 0), or x * scale; fp32 in place.
+__global__ void __launch_bounds__(256)
+scale_softcap_kernel(float* __restrict__ x, long long total, float scale, float cap) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float z = x[i] * scale;
+  x[i] = cap > 0.f ? cap * tanhf(z / cap) : z;
+}
+
+// acc[t, c] += sigmoid(gate[t]) * y[t, c]: gate fp32 with a row pitch, acc and y in the activation type.
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_gate_add_kernel(T* __restrict__ acc, const T* __restrict__ y, const float* __restrict__ gate, long long gate_ld,
+                    long long total, int width) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const float g = sigmoid_f(gate[(i / width) * gate_ld]);
+  acc[i] = from_f32<T>(to_f32<T>(acc[i]) + g * to_f32<T>(y[i]));
 }
 
 template <typename T, int NV>
 static int launch_attention_tiles(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                   const void* atoms, int n_long, const void* tables, int max_blocks, int block_size,
                                   int Hq, int G, int d, int dv, float scale, int chunk, int window, int kpitch,
-                                  int vpitch, cudaStream_t s) {
+                                  int vpitch, const void* dist_bias, int bias_len, const void* gate,
+                                  long long gate_ld, cudaStream_t s) {
   const size_t smem = (size_t)(kBQ * (d + 4) + std::max(kBK * (d + 4), kBQ * (kBK + 4)) + kBK * NV * 64) * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(sink_attention_tile_kernel<T, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return (int)e;
   sink_attention_tile_kernel<T, NV><<<dim3(2 * n_long, Hq), 256, smem, s>>>(
       (const float*)q, (const T*)kcache, (const T*)vcache, (const float*)sink, (T*)out, (const int*)atoms,
-      (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, window, kpitch, vpitch);
+      (const int*)tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, window, kpitch, vpitch,
+      (const float*)dist_bias, bias_len, (const T*)gate, gate_ld);
   return SXB_OK;
 }
 
@@ -1356,8 +1516,10 @@ static int launch_attention_tiles(const void* q, const void* kcache, const void*
 SXB_API int sxb_sink_attention_atoms(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                      const void* atoms, int n_atoms, int n_long, const void* tables, int max_blocks,
                                      int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int window,
-                                     int k_pitch, int v_pitch, int dtype, void* stream) {
+                                     int k_pitch, int v_pitch, const void* dist_bias, int bias_len, const void* gate,
+                                     long long gate_ld, int dtype, void* stream) {
   if (n_atoms <= 0) return SXB_OK;
+  if (dist_bias != nullptr && bias_len < 1) return SXB_ERR_UNSUPPORTED;
   if (k_pitch <= 0) k_pitch = G * d;
   if (v_pitch <= 0) v_pitch = G * dv;
   if (d % 4 || dv % 4 || k_pitch % 4 || v_pitch % 4 || d > 256 || dv > 256 || Hq % G || n_long < 0 || n_long > n_atoms)
@@ -1369,7 +1531,8 @@ SXB_API int sxb_sink_attention_atoms(const void* q, const void* kcache, const vo
 #define TILES(NV)                                                                                                     \
   SEQMIX_DISPATCH(dtype, (rc = launch_attention_tiles<T, NV>(q, kcache, vcache, sink, out, atoms, n_long, tables,      \
                                                               max_blocks, block_size, Hq, G, d, dv, scale, chunk,      \
-                                                              window, k_pitch, v_pitch, s)))
+                                                              window, k_pitch, v_pitch, dist_bias, bias_len, gate,     \
+                                                              gate_ld, s)))
     if (nv == 1) TILES(1);
     else if (nv == 2) TILES(2);
     else if (nv == 3) TILES(3);
@@ -1381,7 +1544,7 @@ SXB_API int sxb_sink_attention_atoms(const void* q, const void* kcache, const vo
   if (n_atoms > n_long) {
     const int rc = attention_rows(dtype, dim3((n_atoms - n_long) * kShortAtom, 1), q, kcache, vcache, sink, out, nullptr,
                                   nullptr, tables, max_blocks, block_size, Hq, G, d, dv, scale, chunk, window, k_pitch,
-                                  v_pitch, (const int*)atoms + 6 * n_long, s);
+                                  v_pitch, (const int*)atoms + 6 * n_long, dist_bias, bias_len, gate, gate_ld, s);
     if (rc != SXB_OK) return rc;
     SXB_CHECK_LAUNCH();
   }
@@ -1640,6 +1803,40 @@ SXB_API int sxb_mlstm_output(const void* o, const void* mt, const void* gate, lo
   SEQMIX_DISPATCH(dtype, (mlstm_output_kernel<T><<<(total + 3) / 4, 128, 0, (cudaStream_t)stream>>>(
                              (const float*)o, (const float*)mt, (const T*)gate, ldg, (const T*)w, (T*)out, n_tokens, H,
                              dv, eps)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Gate of a per-layer token input: out `dtype` [n_tokens, out_w] = gelu_tanh(gx[:, :dim]) * table[ids, col0 : col0 + dim],
+ * zero in the columns dim .. out_w - 1 (padding up to the next product's alignment).  gx rows of pitch ld, table rows of
+ * pitch table_ld. */
+SXB_API int sxb_side_gate(const void* gx, long long ld, const void* table, long long table_ld, const void* ids, void* out,
+                          int n_tokens, int dim, int out_w, int col0, int dtype, void* stream) {
+  const long long total = (long long)n_tokens * out_w;
+  if (total <= 0) return SXB_OK;
+  if (dim > out_w) return SXB_ERR_BAD_ARG;
+  SEQMIX_DISPATCH(dtype, (side_gate_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)gx, ld, (const T*)table, table_ld, (const int*)ids, (T*)out, total, dim, out_w,
+                             col0)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* In place on fp32 x [total]: x * scale, then cap * tanh(. / cap) when cap > 0. */
+SXB_API int sxb_scale_softcap(void* x, long long total, float scale, float cap, void* stream) {
+  if (total <= 0) return SXB_OK;
+  scale_softcap_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float*)x, total, scale, cap);
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* acc `dtype` [rows, width] += sigmoid(gate[row]) * y; gate fp32, one number per row at pitch gate_ld. */
+SXB_API int sxb_row_gate_add(void* acc, const void* y, const void* gate, long long gate_ld, long long rows, int width,
+                             int dtype, void* stream) {
+  const long long total = rows * width;
+  if (total <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (row_gate_add_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                             (T*)acc, (const T*)y, (const float*)gate, gate_ld, total, width)));
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }

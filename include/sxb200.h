@@ -450,7 +450,7 @@ int sxb_int_gemv(const void* x, const void* codes, const void* scale, const void
 int sxb_embed_sinusoid(const void* ids, const void* pos, const void* table, void* out, int n_tokens, int width,
                        float scale, float base, int dtype, void* stream);
 int sxb_resid_norm_step(void* resid, const void* y, const void* w_post, const void* extra, const void* w_pre,
-                        void* out, long long rows, int width, float eps, int dtype, void* stream);
+                        void* out, long long rows, int width, float eps, float mult, int dtype, void* stream);
 int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, void* q_out, void* kcache, void* vcache,
                        const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens, int max_blocks,
                        int block_size, int Hq, int G, int d, int dv, float eps, int normalize, int dtype,
@@ -458,7 +458,8 @@ int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, void* q_
 int sxb_sink_attention(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                        const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens, int max_blocks,
                        int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int window,
-                       int k_pitch, int v_pitch, int dtype, void* stream);
+                       int k_pitch, int v_pitch, const void* dist_bias, int bias_len, const void* gate,
+                       long long gate_ld, int dtype, void* stream);
 int sxb_conv_silu(const void* x, long long ld, const void* w, const void* bias, const void* state,
                   const void* seq_info, const void* tok_seq, void* out, int n_tokens, int C, int taps, int dtype,
                   void* stream);
@@ -480,7 +481,8 @@ int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act
 int sxb_sink_attention_atoms(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                              const void* atoms, int n_atoms, int n_long, const void* tables, int max_blocks,
                              int block_size, int Hq, int G, int d, int dv, float scale, int chunk, int window,
-                             int k_pitch, int v_pitch, int dtype, void* stream);
+                             int k_pitch, int v_pitch, const void* dist_bias, int bias_len, const void* gate,
+                             long long gate_ld, int dtype, void* stream);
 
 /* ---- csrc/moe_ragged.cu */
 /* As sxb_moe_scatter with every copied row multiplied by its routing weight: moe_input[slot(t, k)] = x[t] * scores[t, k].
@@ -513,6 +515,19 @@ int sxb_mlstm_gate_scan(const void* raw_i, const void* raw_f, long long ld, cons
                         int n_seqs, int n_tokens, int H, int dtype, void* stream);
 int sxb_mlstm_output(const void* o, const void* mt, const void* gate, long long ldg, const void* w, void* out,
                      int n_tokens, int H, int dv, float eps, int dtype, void* stream);
+
+/* ---- csrc/seq_mixers.cu */
+int sxb_qkv_filter_norm_append(const void* qkv, long long ld, const void* conv_w, const void* state,
+                               const void* seq_info, const void* q_w, const void* k_w, void* q_out, void* kcache,
+                               void* vcache, const void* tok_seq, const void* tok_pos, const void* tables,
+                               int n_tokens, int max_blocks, int block_size, int Hq, int G, int d, int dv,
+                               int taps, float eps, int normalize, float temp_coef, int temp_every, int dtype,
+                               void* stream);
+int sxb_side_gate(const void* gx, long long ld, const void* table, long long table_ld, const void* ids, void* out,
+                  int n_tokens, int dim, int out_w, int col0, int dtype, void* stream);
+int sxb_scale_softcap(void* x, long long total, float scale, float cap, void* stream);
+int sxb_row_gate_add(void* acc, const void* y, const void* gate, long long gate_ld, long long rows, int width,
+                     int dtype, void* stream);
 
 #ifdef __cplusplus
 }

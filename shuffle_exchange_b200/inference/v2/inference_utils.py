@@ -62,6 +62,7 @@ class ActivationType(IntEnum):
     ReGLU = 4
     SiGLU = 5
     IDENTITY = 6
+    RELU_SQ = 7          # relu(x) ** 2
     InvalidType = -1
 
 

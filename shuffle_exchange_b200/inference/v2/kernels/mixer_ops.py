@@ -18,10 +18,11 @@ from ....native import lib as _lib
 
 _lib.register({
     "sxb_embed_sinusoid": "pppp" "ii" "ff" "i" "p",
-    "sxb_resid_norm_step": "pppppp" "l" "i" "f" "i" "p",
+    "sxb_resid_norm_step": "pppppp" "l" "i" "ff" "i" "p",
     "sxb_qk_norm_append": "p" "l" "ppppppp" "iiiiiii" "f" "ii" "p",
-    "sxb_sink_attention": "pppppppp" "iiiiiii" "f" "iiiii" "p",
-    "sxb_sink_attention_atoms": "pppppp" "ii" "p" "iiiiii" "f" "iiiii" "p",
+    "sxb_qkv_filter_norm_append": "p" "l" "ppppppppppp" "iiiiiiii" "f" "i" "f" "i" "i" "p",
+    "sxb_sink_attention": "pppppppp" "iiiiiii" "f" "iiii" "p" "i" "p" "l" "i" "p",
+    "sxb_sink_attention_atoms": "pppppp" "ii" "p" "iiiiii" "f" "iiii" "p" "i" "p" "l" "i" "p",
     "sxb_conv_silu": "p" "l" "pppppp" "iii" "i" "p",
     "sxb_conv_state_update": "p" "l" "pp" "iii" "i" "p",
     "sxb_unit_norm_heads": "p" "l" "iii" "ff" "i" "p",
@@ -38,6 +39,9 @@ _lib.register({
     "sxb_mlstm_prepare": "p" "l" "p" "iiii" "f" "i" "p",
     "sxb_mlstm_gate_scan": "pp" "l" "pp" "f" "ppppp" "iii" "i" "p",
     "sxb_mlstm_output": "ppp" "l" "pp" "iii" "f" "i" "p",
+    "sxb_side_gate": "p" "l" "p" "l" "pp" "iiii" "i" "p",
+    "sxb_scale_softcap": "p" "l" "ff" "p",
+    "sxb_row_gate_add": "ppp" "l" "l" "i" "i" "p",
 })
 
 _ACTS = {"identity": 0, "relu": 1, "gelu": 2, "silu": 3, "relu_sq": 4}
@@ -81,22 +85,23 @@ def _rms(x: torch.Tensor, eps: float) -> torch.Tensor:
 
 def resid_norm_step(resid: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[torch.Tensor],
                     extra: Optional[torch.Tensor], w_pre: Optional[torch.Tensor], eps: float,
-                    out_dtype: torch.dtype) -> Optional[torch.Tensor]:
-    """In place on the fp32 residual ``[T, W]``: ``+= rms_norm(y) * w_post`` (if ``y``), ``+= extra`` (if given); returns
-    ``rms_norm(residual) * w_pre`` in ``out_dtype`` (None without ``w_pre``).  One pass per row."""
+                    out_dtype: torch.dtype, mult: float = 1.0, copy_out: bool = False) -> Optional[torch.Tensor]:
+    """In place on the fp32 residual ``[T, W]``: ``+= mult * rms_norm(y) * w_post`` (if ``y``; without ``w_post``:
+    ``+= mult * y``), ``+= extra`` (if given); returns ``rms_norm(residual) * w_pre`` in ``out_dtype`` (without ``w_pre``:
+    the residual itself in ``out_dtype`` if ``copy_out``, else None).  One pass per row."""
     T, W = resid.shape
     if resid.is_cuda:
-        out = torch.empty(T, W, dtype=out_dtype, device=resid.device) if w_pre is not None else None
+        out = torch.empty(T, W, dtype=out_dtype, device=resid.device) if (w_pre is not None or copy_out) else None
         code = _lib.dtype_code(out_dtype)
         _lib.call("sxb_resid_norm_step", resid.data_ptr(), _lib.ptr(y), _lib.ptr(w_post), _lib.ptr(extra),
-                  _lib.ptr(w_pre), _lib.ptr(out), T, W, float(eps), code, _lib.stream_ptr())
+                  _lib.ptr(w_pre), _lib.ptr(out), T, W, float(eps), float(mult), code, _lib.stream_ptr())
         return out
     if y is not None:
-        resid += _rms(y.float(), eps) * w_post.float()
+        resid += mult * (_rms(y.float(), eps) * w_post.float() if w_post is not None else y.float())
     if extra is not None:
         resid += extra
     if w_pre is None:
-        return None
+        return resid.to(out_dtype) if copy_out else None
     return (_rms(resid, eps) * w_pre.float()).to(out_dtype)
 
 
@@ -128,6 +133,63 @@ def qk_norm_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], kcache: torc
     return q.contiguous()
 
 
+def qkv_filter_norm_append(qkv: torch.Tensor, conv_w: Optional[torch.Tensor], state: Optional[torch.Tensor],
+                           seq_info: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
+                           kcache: torch.Tensor, vcache: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor,
+                           tables: torch.Tensor, Hq: int, G: int, d: int, dv: int, eps: float, normalize: bool = True,
+                           temp_coef: float = 0.0, temp_every: int = 1) -> torch.Tensor:
+    """:func:`qk_norm_append` for projections ``qkv`` ``[T, >= Hq*d + G*d + G*dv]`` that first pass a short causal filter
+    over time on every channel (``conv_w`` ``[C, taps]``, last column = current token; inputs before this batch's rows
+    from ``state`` ``[slots, taps-1, C]``, before the sequence's start zero; None: no filter -- call
+    :func:`conv_state_update` on the same columns afterwards).  q and k heads are then divided by their root mean square
+    (``normalize``) and multiplied by ``q_w`` / ``k_w`` (``[d]``, shared by the heads; None: no weight); q also by
+    ``1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)``.  Returns q fp32 ``[T, Hq, d]``; k, v go to the caches."""
+    T = qkv.shape[0]
+    bs = kcache.shape[1]
+    C = (Hq + G) * d + G * dv
+    taps = conv_w.shape[1] if conv_w is not None else 1
+    if qkv.is_cuda:
+        q = torch.empty(T, Hq, d, dtype=torch.float32, device=qkv.device)
+        _lib.call("sxb_qkv_filter_norm_append", _rows(qkv).data_ptr(), qkv.stride(0), _lib.ptr(conv_w),
+                  _lib.ptr(state if taps > 1 else None), seq_info.data_ptr(), _lib.ptr(q_w), _lib.ptr(k_w),
+                  q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(),
+                  tables.data_ptr(), T, tables.shape[1], bs, Hq, G, d, dv, taps, float(eps), int(normalize),
+                  float(temp_coef), int(temp_every), _dt(qkv), _lib.stream_ptr())
+        return q
+    x = qkv[:, :C].float()
+    if conv_w is not None:
+        wf = conv_w.float()
+        y = torch.empty_like(x)
+        for first, n, seen, slot in seq_info.tolist():
+            hist = state[slot].float() if (seen > 0 and taps > 1) else torch.zeros(taps - 1, C)
+            if 0 < seen < taps - 1:
+                hist = hist.clone()
+                hist[: taps - 1 - seen] = 0
+            full = torch.cat([hist, x[first: first + n]], dim=0)
+            acc = torch.zeros(n, C)
+            for j in range(taps):
+                acc += wf[:, j] * full[j: j + n]
+            y[first: first + n] = acc
+        x = y
+    q = x[:, : Hq * d].reshape(T, Hq, d)
+    k = x[:, Hq * d: (Hq + G) * d].reshape(T, G, d)
+    v = x[:, (Hq + G) * d:].reshape(T, G, dv)
+    if normalize:
+        q, k = _rms(q, eps), _rms(k, eps)
+    if q_w is not None:
+        q = q * q_w.float()
+    if k_w is not None:
+        k = k * k_w.float()
+    if temp_coef != 0.0:
+        steps = torch.div(tok_pos.long() + 1, int(temp_every), rounding_mode="floor") + 1
+        q = q * (1.0 + temp_coef * torch.log(steps.float()))[:, None, None]
+    page = tables[tok_seq.long(), (tok_pos // bs).long()].long()
+    off = (tok_pos % bs).long()
+    kcache[page, off] = k.to(kcache.dtype)
+    vcache[page, off] = v.to(vcache.dtype)
+    return q.contiguous()
+
+
 SHORT_ATOM = 16          # atoms of at most this many queries run one warp per (query, head)
 
 
@@ -138,7 +200,8 @@ def tiles_supported(d: int, dv: int) -> bool:
 def sink_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, sink: Optional[torch.Tensor],
                    tok_seq: torch.Tensor, tok_pos: torch.Tensor, tables: torch.Tensor, scale: float, chunk: int,
                    out_dtype: torch.dtype, atoms: Optional[torch.Tensor] = None, n_long: int = 0, window: int = 0,
-                   value_cols: int = 0, value_col0: int = 0) -> torch.Tensor:
+                   value_cols: int = 0, value_col0: int = 0, dist_bias: Optional[torch.Tensor] = None,
+                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Softmax attention of each token (fp32 ``q`` ``[T, Hq, d]``) over the cached keys ``lo..pos`` of its sequence,
     ``lo`` = first position of the token's chunk of ``chunk`` positions, or ``pos - window + 1`` (not below 0) for a
     sliding ``window``, or 0 (both 0: plain causal).  ``sink`` (fp32 ``[Hq]``) adds ``exp(sink[h])`` to the
@@ -147,6 +210,9 @@ def sink_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
     ``value_cols = dv > 0``: the values are the ``dv`` columns of the key rows that start at ``value_col0`` (one key
     head; ``vcache`` is not read) -- attention in a latent space where a key is ``[latent | extra]`` and its value the
     latent itself.
+
+    ``dist_bias`` (fp32 ``[Hq, L]``): ``dist_bias[h, min(pos - j, L - 1)]`` is added to the scaled score of key ``j``.
+    ``gate`` (``[T, Hq * dv]``, a column slice is fine): the result is multiplied by ``sigmoid(gate)``.
 
     With the batch's attention ``atoms`` (longest first) of which the first ``n_long`` hold more than
     :data:`SHORT_ATOM` queries, those run the tiled kernel (64 queries per CTA, K/V tiles shared by them) and the rest
@@ -166,15 +232,22 @@ def sink_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
         vptr = vsrc.data_ptr() + (value_col0 * vsrc.element_size() if value_cols > 0 else 0)
         if value_cols > 0 and value_col0 % 8:
             raise ValueError("value columns start at a multiple of 8")
+        if dist_bias is not None and (dist_bias.dtype != torch.float32 or not dist_bias.is_contiguous()
+                                      or dist_bias.shape[0] != Hq):
+            raise ValueError("the distance bias is a contiguous fp32 [heads, distances] table")
+        if gate is not None and gate.dtype != out_dtype:
+            raise ValueError("the gate has the activation dtype")
+        extra = (_lib.ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1],
+                 None if gate is None else _rows(gate).data_ptr(), 0 if gate is None else gate.stride(0))
         if atoms is not None and n_long > 0 and tiles_supported(d, dv):
             _lib.call("sxb_sink_attention_atoms", q.data_ptr(), kcache.data_ptr(), vptr, _lib.ptr(sink),
                       out.data_ptr(), atoms.data_ptr(), atoms.shape[0], int(n_long), tables.data_ptr(), tables.shape[1],
-                      bs, Hq, G, d, dv, float(scale), int(chunk), int(window), 0, v_pitch, _lib.dtype_code(out_dtype),
-                      _lib.stream_ptr())
+                      bs, Hq, G, d, dv, float(scale), int(chunk), int(window), 0, v_pitch, *extra,
+                      _lib.dtype_code(out_dtype), _lib.stream_ptr())
             return out
         _lib.call("sxb_sink_attention", q.data_ptr(), kcache.data_ptr(), vptr, _lib.ptr(sink),
                   out.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), tables.data_ptr(), T, tables.shape[1], bs, Hq,
-                  G, d, dv, float(scale), int(chunk), int(window), 0, v_pitch, _lib.dtype_code(out_dtype),
+                  G, d, dv, float(scale), int(chunk), int(window), 0, v_pitch, *extra, _lib.dtype_code(out_dtype),
                   _lib.stream_ptr())
         return out
     out = torch.empty(T, Hq, dv, dtype=torch.float32)
@@ -190,11 +263,16 @@ def sink_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, 
         else:
             v = vcache[page, js % bs].float().repeat_interleave(rep, dim=1)
         s = torch.einsum("hd,nhd->hn", q[t], k) * scale
+        if dist_bias is not None:
+            s = s + dist_bias[:, (pos - js).clamp(max=dist_bias.shape[1] - 1)]
         if sink is not None:
             s = torch.cat([s, sink.float()[:, None]], dim=1)
         p = torch.softmax(s, dim=-1)[:, : js.numel()]
         out[t] = torch.einsum("hn,nhd->hd", p, v)
-    return out.reshape(T, Hq * dv).to(out_dtype)
+    out = out.reshape(T, Hq * dv)
+    if gate is not None:
+        out = out * torch.sigmoid(gate.float())
+    return out.to(out_dtype)
 
 
 # ------------------------------------------------------------------------------------------------ short convolution
@@ -543,3 +621,47 @@ def mlstm_output(o: torch.Tensor, mt: torch.Tensor, gate: torch.Tensor, w: torch
     den = torch.maximum(oo[:, :, dv].abs(), torch.exp(-mt)) + 1e-6
     h = _rms(oo[:, :, :dv] / den[:, :, None], eps).reshape(T, H * dv)
     return (h * w.float() * torch.sigmoid(gate.float())).to(out_dtype)
+
+
+# ------------------------------------------------------------------------------------------------ small row ops
+def side_gate(gx: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int, dim: int, out_width: int) -> torch.Tensor:
+    """``[T, out_width]``: ``gelu_tanh(gx[:, :dim]) * table[ids, col0 : col0 + dim]``, zero in the columns from ``dim``
+    on (padding for the product that follows).  ``gx`` may be a column slice."""
+    T = gx.shape[0]
+    if gx.is_cuda:
+        out = torch.empty(T, out_width, dtype=gx.dtype, device=gx.device)
+        if table.dtype != gx.dtype:
+            raise ValueError("the table is stored in the activation dtype")
+        _lib.call("sxb_side_gate", _rows(gx).data_ptr(), gx.stride(0), _rows(table).data_ptr(), table.stride(0),
+                  ids.data_ptr(), out.data_ptr(), T, int(dim), int(out_width), int(col0), _dt(gx), _lib.stream_ptr())
+        return out
+    g = torch.nn.functional.gelu(gx[:, :dim].float(), approximate="tanh") * table[ids.long(), col0: col0 + dim].float()
+    out = torch.zeros(T, out_width, dtype=gx.dtype)
+    out[:, :dim] = g.to(gx.dtype)
+    return out
+
+
+def scale_softcap_(x: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+    """In place on fp32 ``x``: ``x * scale``, then ``cap * tanh(x / cap)`` when ``cap > 0``."""
+    if x.is_cuda:
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise ValueError("expected a contiguous fp32 tensor")
+        _lib.call("sxb_scale_softcap", x.data_ptr(), x.numel(), float(scale), float(cap), _lib.stream_ptr())
+        return x
+    x.mul_(scale)
+    if cap > 0:
+        x.copy_(cap * torch.tanh(x / cap))
+    return x
+
+
+def row_gate_add_(acc: torch.Tensor, y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """In place: ``acc[t] += sigmoid(gate[t]) * y[t]``; ``gate`` fp32 ``[T]`` (any stride), ``acc`` / ``y`` ``[T, W]``."""
+    T, W = acc.shape
+    if acc.is_cuda:
+        if gate.dtype != torch.float32 or not acc.is_contiguous() or not y.is_contiguous() or y.dtype != acc.dtype:
+            raise ValueError("expected contiguous rows of one dtype and an fp32 gate")
+        _lib.call("sxb_row_gate_add", acc.data_ptr(), y.data_ptr(), gate.data_ptr(), gate.stride(0), T, W, _dt(acc),
+                  _lib.stream_ptr())
+        return acc
+    acc.copy_((acc.float() + torch.sigmoid(gate.float())[:, None] * y.float()).to(acc.dtype))
+    return acc

@@ -7,7 +7,10 @@ The stack is data (:class:`HybridSpec`), as :class:`~.inference_transformer_base
 transformer family; per-architecture policies (``fomalix/policy.py``) fill it from a checkpoint's configuration and fuse
 the checkpoint's tensors into the projection layouts the mixer modules declare.
 
-Two layer forms (``HybridSpec.block_form``).  ``"sandwich"``: ``x += post_norm(sublayer(pre_norm(x)))``.
+Three layer forms (``HybridSpec.block_form``).  ``"sandwich"``: ``x += post_norm(sublayer(pre_norm(x)))``.
+``"pre_scaled"``: ``x += m * sublayer(pre_norm(x))`` with one multiplier ``m`` for the whole stack, and optionally a
+per-layer token input behind the feed-forward: ``x += m * rms_norm(proj(gelu(gate x) * e))`` where ``e`` is the layer's
+part of one more embedding row of the token (``token_side_dim`` channels per layer).
 ``"post_scaled"``: ``x += scale (.) post_norm(sublayer(x + conv(x)))`` -- no pre-norm, a post-norm with one gain, a
 per-channel scale, a short causal filter with a skip path in front of every sublayer (its last inputs are state of the
 sequence), and optionally the stream handed to the next layer is a learned mixture of the embedding and of all
@@ -32,7 +35,8 @@ from ..inference_utils import ActivationType, DtypeEnum, NormTypeEnum, ceil_div
 from ..kernels import mixer_ops as M
 from ..modules import heuristics
 from ..modules.configs import (DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSRecurrentMixerConfig,
-                               DSSelfAttentionConfig, MaskingType, PositionalEmbeddingType, RotateHalfConfig)
+                               DSSelfAttentionConfig, DistanceBiasConfig, MaskingType, PositionalEmbeddingType,
+                               RotateHalfConfig)
 from ..ragged.kv_cache import KVCacheConfig
 from ..ragged.state_pool import StatePoolConfig
 from .inference_transformer_base import DSInferenceModelBase, LayerWeights
@@ -59,6 +63,7 @@ class HybridLayerSpec:
     top_k: int = 1
     moe_score: str = "softmax"
     moe_weight_input: bool = False
+    moe_renormalize: bool = False               # the chosen experts' scores are divided by their sum
     window: int = 0                             # attention: > 0 = the query and the window - 1 positions before it
     q_rank: int = 0                             # latent attention: query latent, key/value latent, rotated channels
     kv_rank: int = 0
@@ -66,6 +71,17 @@ class HybridLayerSpec:
     rot_dims: int = 0                           # how many of the rot_dim channels turn (in interleaved pairs)
     rot_base: float = 10000.0
     gate_cap: float = 0.0                       # mlstm
+    # attention with filtered projections (``conv_taps`` taps on q | k | v), a weighted q/k norm, a query temperature,
+    # a learned distance-bucket bias (``dist_rows`` table rows, last row from distance ``dist_far`` on) and a gate
+    qk_norm_weight: bool = False
+    q_temp_coef: float = 0.0
+    q_temp_every: int = 1
+    dist_rows: int = 0
+    dist_far: int = 0
+    out_gate: bool = False
+    ff_gated: bool = True                       # moe: experts are down(act(gate) * up); False: down(act(up))
+    router_bias: bool = False
+    shared_ff_dim: int = 0                      # moe: a shared expert of this width, gated by a sigmoid per token
 
 
 @dataclass
@@ -81,7 +97,11 @@ class HybridSpec:
     loop_times: int = 1
     dtype: torch.dtype = torch.bfloat16
     max_seq_len: int = 1 << 20
-    block_form: str = "sandwich"                # "sandwich" | "post_scaled"
+    block_form: str = "sandwich"                # "sandwich" | "post_scaled" | "pre_scaled"
+    residual_mult: float = 1.0                  # pre_scaled: what every sublayer's output is multiplied by
+    token_side_dim: int = 0                     # pre_scaled: channels per layer of the per-layer token input (0: none)
+    logit_scale: float = 1.0
+    logit_softcap: float = 0.0                  # > 0: logits <- cap * tanh(logits / cap)
     input_conv_taps: int = 0                    # post_scaled: taps of the filter in front of every sublayer
     depth_mix: bool = False                     # post_scaled: every layer hands on a mixture of all results so far
 
@@ -150,7 +170,7 @@ class DSHybridModel(DSInferenceModelBase):
             self.post_norm = heuristics.instantiate_scaled_post_norm(DSNormConfig(
                 max_tokens=mt, type=NormTypeEnum.RMSNorm, channels=s.model_dim, residual_dtype=DtypeEnum.fp32,
                 input_dtype=dt, output_dtype=dt, eps=s.norm_eps), ec)
-        elif s.block_form != "sandwich":
+        elif s.block_form not in ("sandwich", "pre_scaled"):
             raise ValueError(f"unknown block form {s.block_form!r}")
         self.mixers, self.moes = [], []
         for L in s.layers:
@@ -159,9 +179,13 @@ class DSHybridModel(DSInferenceModelBase):
                 moe = heuristics.instantiate_moe(DSMoEConfig(
                     max_tokens=mt, model_dim=s.model_dim, intermediate_features=L.ff_dim, n_experts=L.n_experts,
                     top_k=L.top_k, input_dtype=dt, output_dtype=dt,
-                    activation={"silu": ActivationType.SiGLU, "gelu": ActivationType.GEGLU,
-                                "relu": ActivationType.ReGLU}[L.ff_activation],
-                    score_function=L.moe_score, weight_input=L.moe_weight_input, router_dtype=DtypeEnum.fp32), ec)
+                    activation=({"silu": ActivationType.SiGLU, "gelu": ActivationType.GEGLU,
+                                 "relu": ActivationType.ReGLU} if L.ff_gated else
+                                {"silu": ActivationType.SILU, "gelu": ActivationType.GELU, "relu": ActivationType.RELU,
+                                 "relu_sq": ActivationType.RELU_SQ})[L.ff_activation],
+                    normalize_scores=L.moe_renormalize,
+                    score_function=L.moe_score, weight_input=L.moe_weight_input, router_dtype=DtypeEnum.fp32,
+                    router_bias=L.router_bias, shared_features=L.shared_ff_dim), ec)
             self.moes.append(moe)
             if L.kind == "latent_attention":
                 mod = heuristics.instantiate_attention(DSSelfAttentionConfig(
@@ -174,6 +198,20 @@ class DSHybridModel(DSInferenceModelBase):
                                                else PositionalEmbeddingType.none),
                     positional_embedding_config=RotateHalfConfig(theta_base=L.rot_base, rotate_dim=L.rot_dims),
                     qk_norm_eps=s.norm_eps, sink=L.sink, kv_latent_dim=L.kv_rank, rope_head_dim=L.rot_dim), ec)
+            elif L.kind == "attention" and (L.conv_taps > 1 or L.qk_norm_weight or L.dist_rows > 0 or L.out_gate
+                                            or L.q_temp_coef != 0.0):
+                mask = (MaskingType.chunked if L.chunk_size > 0 else
+                        MaskingType.sliding_window if L.window > 0 else MaskingType.causal)
+                mod = heuristics.instantiate_attention(DSSelfAttentionConfig(
+                    max_tokens=mt, n_heads_q=L.n_heads, n_heads_kv=L.n_heads_kv, head_size=L.key_dim,
+                    v_head_size=L.value_dim, max_sequences=sm.max_ragged_sequence_count, scale_factor=L.attn_scale,
+                    input_dtype=dt, output_dtype=dt, masking_type=mask,
+                    masking_args={"size": L.chunk_size or L.window} if mask != MaskingType.causal else {},
+                    positional_embedding_type=(PositionalEmbeddingType.distance_bias if L.dist_rows > 0
+                                               else PositionalEmbeddingType.none),
+                    distance_bias=DistanceBiasConfig(rows=L.dist_rows, far=L.dist_far) if L.dist_rows > 0 else None,
+                    qk_norm_eps=s.norm_eps, qkv_conv_taps=L.conv_taps, qk_norm_weight=L.qk_norm_weight,
+                    q_temp_coef=L.q_temp_coef, q_temp_every=L.q_temp_every, output_gate=L.out_gate), ec)
             elif L.kind == "attention":
                 mod = heuristics.instantiate_attention(DSSelfAttentionConfig(
                     max_tokens=mt, n_heads_q=L.n_heads, n_heads_kv=L.n_heads_kv, head_size=L.key_dim,
@@ -198,6 +236,9 @@ class DSHybridModel(DSInferenceModelBase):
                 self._cache_of_run[r] = n_cache
                 shapes.append((L.n_heads_kv, L.key_dim, L.value_dim))
                 n_cache += 1
+                if hasattr(self.mixers[li], "state_shapes"):        # carried inputs of filtered projections
+                    self._state_of_run[r] = tuple(self._state_cfg.add(shape, sdt)
+                                                  for shape, sdt in self.mixers[li].state_shapes())
             elif L.kind == "latent_attention":
                 self._cache_of_run[r] = n_cache
                 shapes.append((1, self.mixers[li].cache_row, 0))        # latent | rotated key part; no value tensor
@@ -258,6 +299,9 @@ class DSHybridModel(DSInferenceModelBase):
     # ------------------------------------------------------------------------------------------ forward
     def _feed_forward(self, L: HybridLayerSpec, lw: LayerWeights, x: torch.Tensor, li: int = -1) -> torch.Tensor:
         if L.ff_kind == "moe":
+            if L.router_bias or L.shared_ff_dim > 0:
+                return self.moes[li](x, lw.moe_gate, lw.moe_w1, lw.moe_w2, gate_b=lw.moe_gate_b if L.router_bias else None,
+                                     shared=(lw.shared_up, lw.shared_down) if L.shared_ff_dim > 0 else None)
             return self.moes[li](x, lw.moe_gate, lw.moe_w1, lw.moe_w2)
         if L.ff_kind == "biased":
             h = M.bias_act_rows(self.linear(x, lw.w_up), lw.b_up, L.ff_activation)
@@ -272,7 +316,11 @@ class DSHybridModel(DSInferenceModelBase):
     def _mixer(self, r: int, li: int, lw: LayerWeights, x: torch.Tensor, batch) -> torch.Tensor:
         L, mod, sm = self.spec.layers[li], self.mixers[li], self.state_manager
         proj = self.linear(x, lw.w_in)
-        if L.kind == "attention":
+        if L.kind == "attention" and hasattr(mod, "filtered_channels"):
+            states = self._state_of_run.get(r, ())
+            ctx = mod(proj, sm.get_cache(self._cache_of_run[r]), batch, None, lw,
+                      sm.get_state(states[0]) if states else None)
+        elif L.kind == "attention":
             ctx = mod(proj, sm.get_cache(self._cache_of_run[r]), batch, None, lw.b_in, lw.sink)
         elif L.kind == "latent_attention":
             ctx = mod(proj, sm.get_cache(self._cache_of_run[r]), batch, None, lw)
@@ -329,11 +377,56 @@ class DSHybridModel(DSInferenceModelBase):
         h = M.rms_scale_rows(x, rows, W["final_norm_w"], s.norm_eps, s.dtype)
         return self.linear(h, W["unembed"])[:, : s.vocab_size].float()
 
+    def _token_side(self, li: int, lw: LayerWeights, x: torch.Tensor, batch) -> torch.Tensor:
+        """Per-layer token input, before its norm: ``proj(gelu(gate x) * e)`` with ``e`` the layer's ``token_side_dim``
+        channels of the token's row of the side table; ``x`` is the stream in the activation dtype."""
+        s = self.spec
+        gx = self.linear(x, lw.side_gate)
+        g = M.side_gate(gx, self.weights["side_embed"], batch.input_ids(), li * s.token_side_dim, s.token_side_dim,
+                        lw.side_proj.shape[1])
+        return self.linear(g, lw.side_proj)
+
+    @torch.no_grad()
+    def _forward_pre_scaled(self, batch) -> torch.Tensor:
+        """Layers ``x <- x + m mixer(norm1(x))``, ``x <- x + m ff(norm2(x))``, ``x <- x + m rms_norm(side(x)) w``.  The
+        output of a sublayer is added by the kernel that also computes what the next sublayer reads (its norm, or the
+        stream itself in the activation dtype for the token input), so ``y`` below is always one addition behind."""
+        W, s = self.weights, self.spec
+        m = s.residual_mult
+        resid = self.embed(batch, W["embed"])
+        first = resid.clone() if any(again for _, again in self._runs) else None
+        y = post = None                 # pending: resid += m * y (post None) or m * rms_norm(y) * post
+        for r, (li, again) in enumerate(self._runs):
+            lw, L = W["layers"][li], s.layers[li]
+            _, x = self.norm(resid, y, lw.norm1, None, post, first if again else None, m)
+            y, post = self._mixer(r, li, lw, x, batch), None
+            if L.ff_dim > 0:
+                _, x = self.norm(resid, y, lw.norm2, None, None, None, m)
+                y = self._feed_forward(L, lw, x, li)
+            if s.token_side_dim > 0:
+                _, x = self.norm(resid, y, None, None, None, None, m, copy_out=True)
+                y, post = self._token_side(li, lw, x, batch), lw.side_norm
+            if self.layer_outputs is not None:
+                self.norm(resid, y, None, None, post, None, m)
+                y = post = None
+                self.layer_outputs.append(resid.clone())
+        rows = batch.last_token_index().long()
+        if rows.numel() == 0:               # a step that only advances caches and states
+            return torch.empty(0, s.vocab_size, dtype=torch.float32, device=resid.device)
+        resid = resid.index_select(0, rows)
+        _, x = self.norm(resid, None if y is None else y.index_select(0, rows), W["final_norm_w"], None, post, None, m)
+        logits = self.linear(x, W["unembed"])[:, : s.vocab_size].float().contiguous()
+        if s.logit_scale != 1.0 or s.logit_softcap > 0.0:
+            M.scale_softcap_(logits, s.logit_scale, s.logit_softcap)
+        return logits
+
     @torch.no_grad()
     def forward(self, batch) -> torch.Tensor:
         W, s = self.weights, self.spec
         if s.block_form == "post_scaled":
             return self._forward_post_scaled(batch)
+        if s.block_form == "pre_scaled":
+            return self._forward_pre_scaled(batch)
         resid = self.embed(batch, W["embed"])
         first = resid.clone() if any(again for _, again in self._runs) else None
         y = post = None                     # output of the last sublayer and its post-norm weight, not yet added

@@ -12,6 +12,14 @@ class PositionalEmbeddingType(Enum):
     rotate_half = "rotate_half"
     rotate_every_other = "rotate_every_other"
     alibi = "alibi"
+    distance_bias = "distance_bias"    # a learned bias per head and bucket of the distance query - key, added to the score
+
+
+class DistanceBiasConfig(DeepSpeedConfigModel):
+    """Buckets of a learned distance bias: a table with ``rows`` rows per head; distances below ``rows // 2`` have a row
+    each, the others share rows on a logarithmic scale that reaches the last row at ``far``."""
+    rows: int
+    far: int
 
 
 class RotateHalfConfig(DeepSpeedConfigModel):
@@ -52,6 +60,15 @@ class DSSelfAttentionConfig(DSModuleConfig):
     # ``kv_latent_dim + rope_head_dim`` channels per token.
     kv_latent_dim: Optional[int] = None
     rope_head_dim: int = 0
+    # Projections that pass a short causal filter over time (``qkv_conv_taps`` taps per channel of q | k | v; the last
+    # ``taps - 1`` projected rows of a sequence are carried state) before the per-head norm.
+    qkv_conv_taps: int = 1
+    qk_norm_weight: bool = False          # the per-head RMS norm of q and k has a weight of head_size entries each
+    # Query temperature: q at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
+    q_temp_coef: float = 0.0
+    q_temp_every: int = 1
+    distance_bias: Optional[DistanceBiasConfig] = None      # with PositionalEmbeddingType.distance_bias
+    output_gate: bool = False             # the heads' outputs are multiplied by sigmoid of one more projection
 
 
 class DSEmbeddingsConfig(DSModuleConfig):
@@ -86,6 +103,10 @@ class DSMoEConfig(DSModuleConfig):
     score_function: str = "softmax"       # "softmax" over all experts, or "sigmoid" of every expert's own logit
     weight_input: bool = False            # the routing weight scales the expert's input instead of its output
     router_dtype: Optional[DtypeEnum] = None    # dtype of the router product (None: the activation dtype)
+    router_bias: bool = False             # the router logits have a bias
+    # A shared expert of ``shared_features`` channels runs for every token; its output is multiplied by the sigmoid of
+    # one more router row (the row after the experts' rows) and added.
+    shared_features: int = 0
 
 
 class DSNormConfig(DSModuleConfig):

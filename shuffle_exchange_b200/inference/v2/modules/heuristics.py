@@ -21,6 +21,8 @@ def instantiate_attention(attention_config: DSSelfAttentionConfig,
     name = "dense_blocked_attention"
     if not DSSelfAttentionRegistry.registry[name].supports_config(attention_config):
         name = "sink_chunked_attention"       # chunk-local mask, sink logit, q/k unit norm or narrower value heads
+    if not DSSelfAttentionRegistry.registry[name].supports_config(attention_config):
+        name = "filtered_bias_attention"      # filtered projections, weighted q/k norm, distance bias, output gate
     return DSSelfAttentionRegistry.instantiate_config(ConfigBundle(name=name, config=attention_config))
 
 

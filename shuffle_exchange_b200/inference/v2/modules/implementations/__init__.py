@@ -17,6 +17,8 @@
  ``mlstm_mixer``              matrix-memory LSTM: exponential gating with a running maximum around the linear recurrence
  ``fp32_scaled_post_rms``     fp32 stream += scale (.) rms_norm(sublayer output) * gain (+ mixture of all layers' streams)
  ``fp32_sandwich_rms``        fp32 residual += post-norm(sublayer output); next pre-norm, one kernel
+ ``filtered_bias_attention``  q | k | v through a short causal filter with carried inputs, weighted per-head RMS norm,
+                              query temperature, learned distance-bucket bias on the scores, sigmoid output gate
  ``gated_delta_mixer`` / ``ssd_mixer``   short convolutions with carried inputs + linear recurrence with a matrix
                               state per (sequence slot, head) + gated group norm
 =========================  =======================================================================================
@@ -50,7 +52,7 @@ def _dt(x) -> DtypeEnum:
 def _act_name(act: ActivationType) -> str:
     return {ActivationType.GELU: "gelu", ActivationType.RELU: "relu", ActivationType.SILU: "silu",
             ActivationType.GEGLU: "gelu", ActivationType.ReGLU: "relu", ActivationType.SiGLU: "silu",
-            ActivationType.IDENTITY: "identity"}[ActivationType(act)]
+            ActivationType.IDENTITY: "identity", ActivationType.RELU_SQ: "relu_sq"}[ActivationType(act)]
 
 
 def _apply_activation(y: torch.Tensor, bias: Optional[torch.Tensor], act: ActivationType) -> torch.Tensor:
@@ -64,6 +66,8 @@ def _apply_activation(y: torch.Tensor, bias: Optional[torch.Tensor], act: Activa
         return F.gated_act(y, _act_name(act))
     if act == ActivationType.IDENTITY:
         return y if bias is None else y + bias
+    if act == ActivationType.RELU_SQ or (y.is_cuda and y.dtype == torch.float32):
+        return M.bias_act_rows(y, bias, _act_name(act))
     return F.bias_act(y, bias, _act_name(act))
 
 
@@ -246,13 +250,34 @@ class DSMultiGemmMoE(DSMoEBase):
     def transform_moe_mlp_2_param(self, param):
         return _param(param.to(_dt(self._config.input_dtype).torch))      # [E, H, F]
 
-    def forward(self, hidden_states, gate_w, mlp_1_w, mlp_2_w, mlp_1_b=None, mlp_2_b=None) -> torch.Tensor:
+    def _shared(self, out, hidden_states, gate_logit, shared):
+        """``out += sigmoid(gate_logit) * down(act(up(h)))``: the expert every token uses."""
+        w_up, w_down = shared
+        h = _apply_activation(F.linear(hidden_states, w_up), None, self._config.activation)
+        return M.row_gate_add_(out, F.linear(h, w_down)[:, : out.shape[1]].contiguous(), gate_logit)
+
+    def forward(self, hidden_states, gate_w, mlp_1_w, mlp_2_w, mlp_1_b=None, mlp_2_b=None, gate_b=None,
+                shared=None) -> torch.Tensor:
+        """``gate_w`` ``[E (+ 1), H]``: the experts' router rows and, with ``shared_features``, one more row whose logit
+        gates the shared expert ``shared = (w_up [Fs, H], w_down [H, Fs])``; ``gate_b`` the logits' bias."""
         c = self._config
         if c.router_dtype is not None and _dt(c.router_dtype).torch != hidden_states.dtype:
             rd = _dt(c.router_dtype).torch
-            logits = torch.nn.functional.linear(hidden_states.to(rd), gate_w.to(rd))
+            logits = torch.nn.functional.linear(hidden_states.to(rd), gate_w.to(rd), gate_b)
         else:
-            logits = torch.nn.functional.linear(hidden_states, gate_w)
+            logits = torch.nn.functional.linear(hidden_states, gate_w, gate_b)
+        shared_logit = None
+        if c.shared_features > 0:
+            shared_logit = logits[:, c.n_experts].float()
+            logits = logits[:, : c.n_experts].contiguous()
+        out = self._routed(hidden_states, logits, mlp_1_w, mlp_2_w, mlp_1_b, mlp_2_b)
+        if shared_logit is not None:
+            out = self._shared(out, hidden_states, shared_logit, shared)
+        self._output = out
+        return out
+
+    def _routed(self, hidden_states, logits, mlp_1_w, mlp_2_w, mlp_1_b, mlp_2_b) -> torch.Tensor:
+        c = self._config
         scores, assign, offsets, counts = moe_ops.top_k_gating(logits, c.top_k, renormalize=c.normalize_scores,
                                                                score_function=c.score_function)
         from .....moe import fused_ep
@@ -386,6 +411,8 @@ class DSSinkChunkedAttention(DSSelfAttentionBase):
             return False
         if MaskingType(config.masking_type) == MaskingType.chunked and int(config.masking_args.get("size", 0)) < 1:
             return False
+        if config.qkv_conv_taps > 1 or config.qk_norm_weight or config.q_temp_coef != 0.0 or config.output_gate:
+            return False
         return (PositionalEmbeddingType(config.positional_embedding_type) == PositionalEmbeddingType.none
                 and (config.v_head_size or config.head_size) <= 256 and config.n_heads_q % config.n_heads_kv == 0)
 
@@ -443,8 +470,9 @@ class DSScaledSinusoidEmbedding(DSEmbeddingBase):
 @DSPreNormRegistry.register_module
 class DSSandwichRMSNorm(DSPreNormBase):
     """Layers of the form ``x <- x + post_norm(sublayer(pre_norm(x)))`` on an fp32 residual: one kernel closes the
-    previous sublayer (``residual += rms_norm(hidden) * gamma_post``), optionally adds another fp32 stream, and opens the
-    next one (returns ``rms_norm(residual) * gamma``)."""
+    previous sublayer (``residual += mult * rms_norm(hidden) * gamma_post``; without ``gamma_post`` the sublayer has no
+    post-norm: ``residual += mult * hidden``), optionally adds another fp32 stream, and opens the next one (returns
+    ``rms_norm(residual) * gamma``; without ``gamma``: the stream itself in the output dtype if ``copy_out``)."""
 
     @staticmethod
     def name() -> str:
@@ -454,9 +482,9 @@ class DSSandwichRMSNorm(DSPreNormBase):
     def supports_config(config: DSNormConfig) -> bool:
         return NormTypeEnum(config.type) == NormTypeEnum.RMSNorm and _dt(config.residual_dtype) == DtypeEnum.fp32
 
-    def forward(self, residual, hidden_states, gamma, beta=None, gamma_post=None, extra=None):
+    def forward(self, residual, hidden_states, gamma, beta=None, gamma_post=None, extra=None, mult=1.0, copy_out=False):
         y = M.resid_norm_step(residual, hidden_states, gamma_post, extra, gamma, self._config.eps,
-                              _dt(self._config.output_dtype).torch)
+                              _dt(self._config.output_dtype).torch, mult, copy_out)
         return residual, y
 
 
@@ -726,3 +754,107 @@ class DSScaledPostRMSNorm(DSPostNormBase):
             stack, n_prev, w, mixed = mix
             M.post_norm_mix(residual, hidden_states, gamma, scale, out, self._config.eps, stack, n_prev, w, mixed)
         return out
+
+
+@DSSelfAttentionRegistry.register_module
+class DSFilteredBiasAttention(DSSelfAttentionBase):
+    """Softmax attention without rotation whose projections pass a short causal filter over time.  Projection columns:
+    ``q (Hq d) | k (G d) | v (G dv) | gate (Hq dv)``.  Every channel of q | k | v is filtered over the sequence (the last
+    ``taps - 1`` projected rows are carried per sequence), q and k heads are RMS-normed with one weight of ``d`` entries
+    each, q is multiplied by ``1 + coef * ln(floor((pos + 1) / every) + 1)``; a key at distance ``n`` behind the query
+    adds the learned ``bias[bucket(n), h]`` to its scaled score (buckets: one per distance below half the table's rows,
+    logarithmic up to ``far`` above); causal or chunk-local / sliding-window mask; the heads' outputs are multiplied by
+    ``sigmoid(gate)``.  Filter sums, norms, temperature, scores, weights and the weighted sum are fp32; the paged cache
+    holds the normalised keys and the filtered values in the activation dtype.
+
+    ``forward(projected, (keys, values), batch, inv_freqs, weights, conv_state)``: ``weights`` has ``conv_w`` ``[C,
+    taps]`` (or None), ``q_norm`` / ``k_norm`` (or None) and ``dist_bias`` (fp32 ``[Hq, distances]`` from
+    :meth:`expand_distance_bias`, or None)."""
+
+    @staticmethod
+    def name() -> str:
+        return "filtered_bias_attention"
+
+    @staticmethod
+    def supports_config(config: DSSelfAttentionConfig) -> bool:
+        if config.kv_latent_dim is not None or config.sink:
+            return False
+        if MaskingType(config.masking_type) not in (MaskingType.causal, MaskingType.chunked, MaskingType.sliding_window):
+            return False
+        pe = PositionalEmbeddingType(config.positional_embedding_type)
+        if pe == PositionalEmbeddingType.distance_bias:
+            b = config.distance_bias
+            if b is None or b.rows < 2 or b.far <= b.rows // 2:
+                return False
+        elif pe != PositionalEmbeddingType.none:
+            return False
+        return (config.head_size <= 256 and (config.v_head_size or config.head_size) <= 256
+                and config.n_heads_q % config.n_heads_kv == 0 and 1 <= config.qkv_conv_taps <= 16
+                and config.q_temp_every >= 1)
+
+    @property
+    def kv_block_size(self) -> int:
+        return 64
+
+    @property
+    def q_block_size(self) -> int:
+        return 1
+
+    @property
+    def filtered_channels(self) -> int:
+        c = self._config
+        return (c.n_heads_q + c.n_heads_kv) * c.head_size + c.n_heads_kv * (c.v_head_size or c.head_size)
+
+    @property
+    def projection_width(self) -> int:
+        c = self._config
+        return self.filtered_channels + (c.n_heads_q * (c.v_head_size or c.head_size) if c.output_gate else 0)
+
+    def state_shapes(self):
+        """[(shape per sequence, dtype)]: the filter's carried inputs (none for a single tap)."""
+        c = self._config
+        if c.qkv_conv_taps <= 1:
+            return []
+        return [((c.qkv_conv_taps - 1, self.filtered_channels), _dt(c.input_dtype).torch)]
+
+    @staticmethod
+    def bucket_of_distance(rows: int, far: int) -> torch.Tensor:
+        """int64 ``[far + 1]``: the table row of every distance ``0 .. far``; larger distances use the last entry (the
+        last row).  ``bucket(n) = n`` below ``half = rows // 2``, else ``min(rows - 1, half + floor(ln(n / half) /
+        ln(far / half) * (rows - half)))``."""
+        half = rows // 2
+        n = torch.arange(far + 1, dtype=torch.float64)
+        ratio = torch.log(n.clamp(min=1) / max(half, 1)) / math.log(far / max(half, 1)) * (rows - half)
+        large = (half + torch.floor(ratio + 1e-9).long()).clamp(max=rows - 1)
+        return torch.where(n < half, n.long(), large)
+
+    @staticmethod
+    def expand_distance_bias(table: torch.Tensor, far: int) -> torch.Tensor:
+        """A checkpoint's ``[rows, Hq]`` table as fp32 ``[Hq, far + 1]`` indexed by the distance itself."""
+        idx = DSFilteredBiasAttention.bucket_of_distance(table.shape[0], far).to(table.device)
+        return table.float().index_select(0, idx).t().contiguous()
+
+    def forward(self, projected: torch.Tensor, kv_cache, batch, inv_freqs=None, weights=None,
+                conv_state=None) -> torch.Tensor:
+        c = self._config
+        dv = c.v_head_size or c.head_size
+        keys, values = kv_cache
+        C = self.filtered_channels
+        t2s, pos, tables, info = batch.token_to_seq(), batch.token_positions(), batch.block_tables(), batch.seq_info()
+        conv_w = weights.conv_w if c.qkv_conv_taps > 1 else None
+        q = M.qkv_filter_norm_append(projected, conv_w, conv_state, info, weights.q_norm if c.qk_norm_weight else None,
+                                     weights.k_norm if c.qk_norm_weight else None, keys, values, t2s, pos, tables,
+                                     c.n_heads_q, c.n_heads_kv, c.head_size, dv, c.qk_norm_eps, True, c.q_temp_coef,
+                                     c.q_temp_every)
+        if conv_w is not None:
+            M.conv_state_update(projected[:, :C], conv_state, info)
+        mt = MaskingType(c.masking_type)
+        chunk = int(c.masking_args["size"]) if mt == MaskingType.chunked else 0
+        window = int(c.masking_args["size"]) if mt == MaskingType.sliding_window else 0
+        atoms, n_long = None, 0
+        if q.is_cuda and M.tiles_supported(c.head_size, dv) and hasattr(batch, "atoms_longer_than"):
+            atoms, n_long = batch.atoms(), batch.atoms_longer_than(M.SHORT_ATOM)
+        bias = weights.dist_bias if c.distance_bias is not None else None
+        gate = projected[:, C: C + c.n_heads_q * dv] if c.output_gate else None
+        return M.sink_attention(q, keys, values, None, t2s, pos, tables, c.scale_factor, chunk, _dt(c.output_dtype).torch,
+                                atoms, n_long, window=window, dist_bias=bias, gate=gate)

@@ -49,6 +49,13 @@ def distance_bucket(n: int, rows: int, far: int) -> int:
     return min(rows - 1, half + int(math.floor(r + 1e-9)))
 
 
+def distance_bias_matrix(column: torch.Tensor, T: int, far: int) -> torch.Tensor:
+    """[T, T]: entry (i, j) is the table entry of distance i - j for j <= i (0 above the diagonal)."""
+    per_distance = torch.stack([column[distance_bucket(n, column.shape[0], far)] for n in range(T)])
+    i = torch.arange(T)
+    return per_distance[(i[:, None] - i[None, :]).clamp(min=0)]
+
+
 def query_temperature(p: int, coef: float, every: int) -> float:
     return 1.0 + coef * math.log(((p + 1) // every) + 1)
 
@@ -69,14 +76,14 @@ def attention_mixer(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict, eps: f
         q = q * temp[:, None, None]
     rel = P.get("rel")
     out = torch.zeros(T, H, dv, dtype=F64)
+    causal = torch.tril(torch.ones(T, T, dtype=torch.bool))
     for hq in range(H):
         g = hq // (H // G)
-        for i in range(T):
-            s = (k[: i + 1, g] @ q[i, hq]) * float(m["scale"])
-            if rel is not None:
-                s = s + torch.stack([rel[distance_bucket(i - j, rel.shape[0], int(m["bias_max"])), hq]
-                                     for j in range(i + 1)])
-            out[i, hq] = torch.softmax(s, dim=0) @ v[: i + 1, g]
+        s = (q[:, hq] @ k[:, g].T) * float(m["scale"])
+        if rel is not None:
+            s = s + distance_bias_matrix(rel[:, hq], T, int(m["bias_max"]))
+        w = torch.softmax(s.masked_fill(~causal, float("-inf")), dim=-1)
+        out[:, hq] = w @ v[:, g]
     ctx = out.reshape(T, H * dv) * torch.sigmoid(h @ P["g"].T)
     return ctx @ P["o"].T
 
@@ -150,3 +157,47 @@ def forward(config: Dict, tensors: Dict[str, torch.Tensor], tokens: List[int], l
     z = (x @ tensors["head"].to(F64).T) * float(config["logit_scale"])
     cap = config.get("logit_softcap")
     return cap * torch.tanh(z / cap) if cap else z
+
+
+def random_weights(config: Dict, seed: int = 0, rel_rows: int = 8) -> Dict[str, torch.Tensor]:
+    """Random tensors under the checkpoint's names (float32); ``rel_rows``: rows of every distance table."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = int(config["width"]), int(config["vocab"])
+    side = config.get("token_side")
+    n_layers = len(config["layers"])
+
+    def lin(o, i):
+        return torch.randn(o, i, generator=g) / math.sqrt(i)
+
+    def gain(n):
+        return 1.0 + 0.2 * torch.randn(n, generator=g)
+
+    T = {"embed": torch.randn(V, W, generator=g), "head": lin(V, W), "final.norm": gain(W)}
+    if side:
+        T["side.embed"] = torch.randn(V, n_layers * int(side["dim"]), generator=g)
+    for i, L in enumerate(config["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+        T[p + "norm1"] = gain(W)
+        for name, rows in (("q", H * d), ("k", G * d), ("v", G * dv)):
+            T[p + "mix." + name] = lin(rows, W)
+            if int(m.get("conv", 1)) > 1:
+                T[p + "mix." + name + ".conv"] = torch.randn(rows, int(m["conv"]), generator=g) * 0.6
+        T[p + "mix.q.norm"], T[p + "mix.k.norm"] = gain(d), gain(d)
+        T[p + "mix.rel"] = torch.randn(rel_rows, H, generator=g)
+        T[p + "mix.g"], T[p + "mix.o"] = lin(H * dv, W), lin(W, H * dv)
+        mlp = L.get("mlp")
+        if mlp is not None:
+            T[p + "norm2"] = gain(W)
+            E, Fe = int(mlp["router"]["experts"]), int(mlp["expert"]["ff"])
+            T[p + "mlp.router"], T[p + "mlp.router.b"] = lin(E, W) * 2, torch.randn(E, generator=g)
+            for e in range(E):
+                T[f"{p}mlp.e{e}.up"], T[f"{p}mlp.e{e}.down"] = lin(Fe, W), lin(W, Fe)
+            if mlp.get("shared"):
+                Fs = int(mlp["shared"]["ff"])
+                T[p + "mlp.shared.up"], T[p + "mlp.shared.down"] = lin(Fs, W), lin(W, Fs)
+                T[p + "mlp.shared.sg"] = lin(1, W) * 2
+        if side:
+            ds = int(side["dim"])
+            T[p + "side.gate"], T[p + "side.proj"], T[p + "side.norm"] = lin(ds, W), lin(W, ds), gain(W)
+    return T

@@ -1,0 +1,492 @@
+"""Ridazen in the ragged engine against the plain evaluation in ``ridazen_oracle.py`` (float64, whole sequences, no cache):
+every mechanism alone, prefill against token-by-token decoding, prompt portions down to two tokens, unequal batches,
+reuse of cache pages and state slots, keys far back, at page borders and on both sides of every edge of the distance
+buckets, the first tokens, long decoding, other sizes, and greedy generation through the scheduler.  Runs on the PyTorch
+branch of every op without a GPU; ``test_ridazen_gpu.py`` runs the same cases on the CUDA kernels."""
+import copy
+import math
+
+import pytest
+import torch
+
+import ridazen_oracle as O
+from shuffle_exchange_b200.inference.v2.config_v2 import RaggedInferenceEngineConfig
+from shuffle_exchange_b200.inference.v2.engine_factory import build_engine_from_state_dict
+from shuffle_exchange_b200.inference.v2.inference_utils import ActivationType, DtypeEnum
+from shuffle_exchange_b200.inference.v2.kernels import mixer_ops as M
+from shuffle_exchange_b200.inference.v2.modules import heuristics
+from shuffle_exchange_b200.inference.v2.modules.configs import DSMoEConfig
+from shuffle_exchange_b200.inference.v2.modules.implementations import DSFilteredBiasAttention
+from shuffle_exchange_b200.inference.v2.ragged.ragged_manager import DSStateManagerConfig
+from shuffle_exchange_b200.inference.v2.scheduler import generate
+
+DEV = "cuda" if torch.cuda.is_available() else "cpu"
+
+MOE = {"expert": {"ff": 16}, "kind": "moe", "router": {"experts": 5, "top": 2}, "shared": {"ff": 12}}
+ATT = {"type": "attention",
+       "mixer": {"bias_max": 40, "conv": 3, "dim": 8, "heads": 4, "kv_heads": 2, "q_temp": {"coef": 0.4, "every": 5},
+                 "scale": 0.3, "vdim": 12},
+       "mlp": MOE}
+
+
+def make_cfg(layers, width=24, vocab=53, side=6, loop=None, mult=0.4, eps=1e-5, logit_scale=0.5, softcap=8.0):
+    return {"architecture": "Ridazen", "layers": copy.deepcopy(layers), "logit_scale": logit_scale,
+            "logit_softcap": softcap, "loop": loop, "norm": {"eps": eps}, "residual_mult": mult,
+            "token_side": {"dim": side} if side else None, "vocab": vocab, "width": width}
+
+
+STACK = make_cfg([ATT, dict(ATT, mlp=None), dict(ATT, mixer=dict(ATT["mixer"], conv=2, kv_heads=4, vdim=8)), ATT],
+                 loop={"start": 1, "stop": 3, "times": 2})
+
+
+def make_engine(cfg, W, dtype=torch.float32, blocks=64, block_size=4, max_live=4, max_tokens=256):
+    sm = DSStateManagerConfig(max_tracked_sequences=max_live, max_ragged_sequence_count=max_live,
+                              max_ragged_batch_size=max_tokens, max_context=blocks * block_size, num_kv_blocks=blocks)
+    return build_engine_from_state_dict(cfg, W, RaggedInferenceEngineConfig(state_manager=sm, kv_block_size=block_size),
+                                        dtype=dtype)
+
+
+def tokens(n, vocab, seed):
+    return torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed)).tolist()
+
+
+def feed(engine, uid, toks, sizes):
+    """Give ``toks`` to the engine in portions of the given sizes (cycled); returns the logits of every token."""
+    out, lo, i = [], 0, 0
+    while lo < len(toks):
+        n = min(sizes[i % len(sizes)], len(toks) - lo)
+        i += 1
+        out.append(engine.put([uid], [torch.tensor(toks[lo: lo + n])], logit_positions=[list(range(n))]))
+        lo += n
+    return torch.cat(out).double().cpu()
+
+
+def close(got, want, tol=2e-4):
+    """Difference with the mean over the vocabulary taken off, relative to the spread of the expected logits."""
+    d = got - want
+    d = d - d.mean(-1, keepdim=True)
+    err = d.pow(2).mean(-1).sqrt() / want.std()
+    assert err.max() < tol, f"worst row {int(err.argmax())}: {float(err.max()):.3e}"
+
+
+@pytest.fixture(scope="module")
+def stack():
+    W = O.random_weights(STACK, seed=4)
+    toks = tokens(47, STACK["vocab"], 5)
+    return W, toks, O.forward(STACK, W, toks)
+
+
+# ------------------------------------------------------------------------------------------------ single mechanisms
+@pytest.mark.parametrize("rows,far", [(8, 40), (32, 256), (6, 100), (7, 50), (2, 5), (64, 4096), (16, 17)])
+def test_distance_buckets(rows, far):
+    """Exact rows below half the table, logarithmic rows above, the last row from ``far`` on; (32, 256) and (64, 4096)
+    have distances whose logarithm ratio is a whole number, which must land in the row that number names."""
+    got = DSFilteredBiasAttention.bucket_of_distance(rows, far).tolist()
+    assert got == [O.distance_bucket(n, rows, far) for n in range(far + 1)]
+    assert got[far] == rows - 1 and got[: rows // 2] == list(range(rows // 2))
+    assert all(a <= b for a, b in zip(got, got[1:]))
+    if (rows, far) == (32, 256):
+        assert got[32] == 16 + 4 and got[31] == 16 + 3 and got[64] == 16 + 8 and got[63] == 16 + 7
+    table = torch.arange(rows * 3, dtype=torch.float32).view(rows, 3)
+    wide = DSFilteredBiasAttention.expand_distance_bias(table, far)
+    assert wide.shape == (3, far + 1) and wide[1, far] == table[rows - 1, 1] and wide[2, 0] == table[0, 2]
+
+
+def _filter_ops(proj, conv_w, q_w, k_w, Hq, G, d, dv, eps, coef, every, cuts, block_size=4, slot=1):
+    """Filter + norm + temperature + cache append in portions; returns q of every token and the cached keys / values."""
+    T, C = proj.shape[0], (Hq + G) * d + G * dv
+    taps = conv_w.shape[1] if conv_w is not None else 1
+    pages = (T + block_size - 1) // block_size
+    kc = torch.full((pages + 1, block_size, G, d), 9.0, device=DEV)
+    vc = torch.full((pages + 1, block_size, G, dv), 9.0, device=DEV)
+    state = torch.full((3, max(taps - 1, 0), C), 7.0, device=DEV)      # what a previous owner of the slot left
+    tables = torch.arange(pages, 0, -1, dtype=torch.int32, device=DEV).view(1, pages)      # pages in reverse order
+    qs, lo = [], 0
+    for n in cuts:
+        info = torch.tensor([[0, n, lo, slot]], dtype=torch.int32, device=DEV)
+        p = proj[lo: lo + n].to(DEV).contiguous()
+        t2s = torch.zeros(n, dtype=torch.int32, device=DEV)
+        pos = torch.arange(lo, lo + n, dtype=torch.int32, device=DEV)
+        qs.append(M.qkv_filter_norm_append(p, None if conv_w is None else conv_w.to(DEV), state, info,
+                                           None if q_w is None else q_w.to(DEV), None if k_w is None else k_w.to(DEV), kc,
+                                           vc, t2s, pos, tables, Hq, G, d, dv, eps, True, coef, every).cpu())
+        if taps > 1:
+            M.conv_state_update(p[:, :C], state, info)
+        lo += n
+    order = tables[0].long().cpu()
+    keys = kc.cpu()[order].reshape(-1, G, d)[:T]
+    vals = vc.cpu()[order].reshape(-1, G, dv)[:T]
+    assert taps == 1 or torch.all(state[[0, 2]] == 7.0)
+    return torch.cat(qs).double(), keys.double(), vals.double()
+
+
+@pytest.mark.parametrize("taps,Hq,G,d,dv", [(3, 4, 2, 8, 12), (1, 2, 2, 5, 3), (5, 3, 1, 40, 36), (2, 1, 1, 4, 4)])
+def test_filtered_projections_norm_and_temperature(taps, Hq, G, d, dv):
+    """Portions shorter than the filter first, a state slot with another sequence's leftovers, pages in reverse order;
+    the temperature changes at the positions where (p + 1) reaches a multiple of ``every``."""
+    g = torch.Generator().manual_seed(taps)
+    T, eps, coef, every = 23, 1e-5, 0.7, 4
+    C = (Hq + G) * d + G * dv
+    proj = torch.randn(T, C + Hq * dv, generator=g)
+    conv = torch.randn(C, taps, generator=g) if taps > 1 else None
+    q_w, k_w = torch.randn(d, generator=g), torch.randn(d, generator=g)
+    u = proj[:, :C].double()
+    f = O.causal_filter(u, conv.double()) if conv is not None else u
+    want_q = O.rms_norm(f[:, : Hq * d].reshape(T, Hq, d), q_w.double(), eps)
+    want_q = want_q * torch.tensor([O.query_temperature(p, coef, every) for p in range(T)])[:, None, None]
+    want_k = O.rms_norm(f[:, Hq * d: (Hq + G) * d].reshape(T, G, d), k_w.double(), eps)
+    want_v = f[:, (Hq + G) * d:].reshape(T, G, dv)
+    assert O.query_temperature(2, coef, every) == 1.0 and O.query_temperature(3, coef, every) == 1.0 + coef * math.log(2)
+    for cuts in ([T], [1, 1, 2, 1, 7, 11]):
+        q, k, v = _filter_ops(proj, conv, q_w, k_w, Hq, G, d, dv, eps, coef, every, cuts)
+        assert torch.allclose(q, want_q, atol=2e-5), float((q - want_q).abs().max())
+        assert torch.allclose(k, want_k, atol=2e-5) and torch.allclose(v, want_v, atol=2e-5)
+    q, _, _ = _filter_ops(proj, conv, None, None, Hq, G, d, dv, eps, 0.0, 1, [T])
+    assert torch.allclose(q, O.rms_norm(f[:, : Hq * d].reshape(T, Hq, d), None, eps), atol=2e-5)
+
+
+def _weights_of_attention(q, bias, block_size, pos0=0, T=None, gate=None):
+    """Attention weights of ``q`` ``[Tq, H, d]`` (positions ``pos0 ..``) over ``T`` cached keys whose rows are one-hot,
+    so the output is the weights themselves; keys are all zero but for one score channel."""
+    Tq, H, d = q.shape
+    pages = (T + block_size - 1) // block_size
+    dv = (T + 3) // 4 * 4
+    keys = torch.zeros(pages * block_size, 1, d)
+    keys[:, 0, 0] = 1.0
+    vals = torch.zeros(pages * block_size, 1, dv)
+    vals[:T, 0, :T] = torch.eye(T)
+    kc, vc = keys.view(pages, block_size, 1, d).to(DEV), vals.view(pages, block_size, 1, dv).to(DEV)
+    tables = torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages)
+    pos = torch.arange(pos0, pos0 + Tq, dtype=torch.int32, device=DEV)
+    atoms, n_long = None, 0
+    if DEV == "cuda" and Tq > M.SHORT_ATOM and d % 4 == 0:
+        atoms = torch.tensor([[0, r0, min(64, Tq - r0), pos0 + r0, 0, 0] for r0 in range(0, Tq, 128)], dtype=torch.int32,
+                             device=DEV)
+        # atoms hold up to 128 queries: two tiles of 64
+        atoms[:, 2] = torch.tensor([min(128, Tq - r0) for r0 in range(0, Tq, 128)], dtype=torch.int32)
+        n_long = atoms.shape[0]
+    out = M.sink_attention(q.to(DEV), kc, vc, None, torch.zeros(Tq, dtype=torch.int32, device=DEV), pos, tables, 1.0, 0,
+                           torch.float32, atoms, n_long, dist_bias=None if bias is None else bias.to(DEV),
+                           gate=None if gate is None else gate.to(DEV))
+    return out.cpu().view(Tq, H, dv)[:, :, :T]
+
+
+@pytest.mark.parametrize("rows,far,block_size,T", [(8, 40, 4, 70), (6, 100, 16, 150), (32, 256, 64, 300), (2, 5, 8, 30)])
+def test_a_bucket_bias_decides_which_keys_are_seen(rows, far, block_size, T):
+    """Keys score alike but for the learned bias.  With one table row far above the rest, a query's weight lies on exactly
+    the keys whose distance falls in that row's bucket: at its nearest and farthest distance, one step outside on either
+    side, hundreds of positions back, beyond ``far``, across page borders -- as a row of a prompt and as a single token."""
+    H = 2
+    bucket = DSFilteredBiasAttention.bucket_of_distance(rows, far).tolist()
+    q = torch.zeros(T, H, 4)
+    for row in sorted({0, 1, rows // 2 - 1, rows // 2, rows // 2 + 1, rows - 2, rows - 1} & set(range(rows))):
+        table = torch.zeros(rows, H)
+        table[row, 0] = 40.0
+        table[(row + 1) % rows, 1] = 40.0
+        bias = DSFilteredBiasAttention.expand_distance_bias(table, far)
+        whole = _weights_of_attention(q, bias, block_size, 0, T)
+        for i in sorted({0, 1, rows // 2, far - 1, far, far + 1, T - 1}):
+            if i >= T:
+                continue
+            alone = _weights_of_attention(q[i: i + 1], bias, block_size, i, T)[0]
+            for w in (whole[i], alone):
+                assert torch.allclose(w.sum(-1), torch.ones(H), atol=1e-5) and w[:, i + 1:].abs().sum() == 0
+                for h, r in ((0, row), ((1, (row + 1) % rows))):
+                    inside = [j for j in range(i + 1) if bucket[min(i - j, far)] == r]
+                    if inside:
+                        assert w[h, inside].sum() > 0.999, (row, i, h)
+                        assert torch.allclose(w[h, inside], torch.full((len(inside),), 1.0 / len(inside)), atol=1e-4)
+
+
+def test_bias_is_added_after_the_scale_and_gate_multiplies_the_output():
+    g = torch.Generator().manual_seed(2)
+    T, H, d, rows, far = 21, 3, 4, 6, 11
+    q = torch.zeros(T, H, d)
+    q[:, :, 0] = torch.randn(T, H, generator=g)              # every key's score channel is 1: score = q[..., 0]
+    table = torch.randn(rows, H, generator=g)
+    gate = torch.randn(T, H * ((T + 3) // 4 * 4), generator=g)
+    bias = DSFilteredBiasAttention.expand_distance_bias(table, far)
+    got = _weights_of_attention(q, bias, 4, 0, T)
+    for h in range(H):
+        s = O.distance_bias_matrix(table[:, h].double(), T, far)     # equal scores drop out of the softmax
+        want = torch.softmax(s.masked_fill(~torch.tril(torch.ones(T, T, dtype=torch.bool)), float("-inf")), -1)
+        assert torch.allclose(got[:, h].double(), want, atol=1e-5)
+    gated = _weights_of_attention(q, bias, 4, 0, T, gate=gate)
+    dvp = (T + 3) // 4 * 4
+    assert torch.allclose(gated, got * torch.sigmoid(gate).view(T, H, dvp)[:, :, :T], atol=1e-5)
+
+
+@pytest.mark.parametrize("E,K,shared", [(5, 2, 12), (4, 4, 0), (6, 1, 8), (3, 2, 5)])
+def test_experts_router_bias_and_shared_expert(E, K, shared):
+    """The largest logits INCLUDING the bias choose; weights are the softmax over the chosen logits; a bias of +30 on one
+    expert puts it into every token's choice; the shared expert's gate is one sigmoid per token."""
+    g = torch.Generator().manual_seed(E)
+    T, W, Fe = 17, 16, 10
+    h = torch.randn(T, W, generator=g)
+    P = {"router": torch.randn(E, W, generator=g), "router.b": torch.randn(E, generator=g)}
+    P["router.b"][E - 1] += 30.0
+    for e in range(E):
+        P[f"e{e}.up"], P[f"e{e}.down"] = torch.randn(Fe, W, generator=g) / 4, torch.randn(W, Fe, generator=g) / 4
+    mlp = {"router": {"experts": E, "top": K}, "expert": {"ff": Fe}, "shared": {"ff": shared} if shared else None}
+    if shared:
+        P["shared.up"], P["shared.down"] = torch.randn(shared, W, generator=g) / 4, torch.randn(W, shared, generator=g) / 4
+        P["shared.sg"] = torch.randn(1, W, generator=g)
+    want = O.moe_ff(h.double(), {k: v.double() for k, v in P.items()}, mlp)
+    mod = heuristics.instantiate_moe(DSMoEConfig(
+        max_tokens=64, model_dim=W, intermediate_features=Fe, n_experts=E, top_k=K, input_dtype=DtypeEnum.fp32,
+        output_dtype=DtypeEnum.fp32, activation=ActivationType.RELU_SQ, normalize_scores=True, router_dtype=DtypeEnum.fp32,
+        router_bias=True, shared_features=shared), None)
+    gate = torch.cat([P["router"]] + ([P["shared.sg"]] if shared else []))
+    gate_b = torch.cat([P["router.b"]] + ([torch.zeros(1)] if shared else []))
+    got = mod(h.to(DEV), gate.to(DEV), torch.stack([P[f"e{e}.up"] for e in range(E)]).to(DEV),
+              torch.stack([P[f"e{e}.down"] for e in range(E)]).to(DEV), gate_b=gate_b.to(DEV),
+              shared=(P["shared.up"].to(DEV), P["shared.down"].to(DEV)) if shared else None)
+    assert torch.allclose(got.double().cpu(), want, atol=2e-4, rtol=1e-4), float((got.double().cpu() - want).abs().max())
+    z = h @ P["router"].T + P["router.b"]
+    assert bool((torch.topk(z, K).indices == E - 1).any(-1).all())
+
+
+def test_residual_step_with_multiplier_token_input_and_soft_cap():
+    g = torch.Generator().manual_seed(11)
+    T, W, dim, V = 7, 20, 6, 13
+    x = torch.randn(T, W, generator=g)
+    y, w_post, w_pre, extra = (torch.randn(T, W, generator=g), torch.randn(W, generator=g), torch.randn(W, generator=g),
+                               torch.randn(T, W, generator=g))
+    eps, m = 1e-4, 0.3
+    r = x.clone().to(DEV)
+    out = M.resid_norm_step(r, y.to(DEV), None, extra.to(DEV), w_pre.to(DEV), eps, torch.float32, m)
+    want = x.double() + m * y.double() + extra.double()
+    assert torch.allclose(r.double().cpu(), want, atol=1e-5)
+    assert torch.allclose(out.double().cpu(), O.rms_norm(want, w_pre.double(), eps), atol=1e-5)
+    r = x.clone().to(DEV)
+    out = M.resid_norm_step(r, y.to(DEV), w_post.to(DEV), None, None, eps, torch.float32, m, copy_out=True)
+    want = x.double() + m * O.rms_norm(y.double(), w_post.double(), eps)
+    assert torch.allclose(r.double().cpu(), want, atol=1e-5) and torch.allclose(out.double().cpu(), want, atol=1e-5)
+    assert M.resid_norm_step(r, None, None, None, None, eps, torch.float32, m) is None
+    # per-layer token input: the layer's own channels of the token's row
+    toks = tokens(T, V, 3)
+    table = torch.randn(V, 3 * dim, generator=g)
+    P = {"gate": torch.randn(dim, W, generator=g), "proj": torch.randn(W, dim, generator=g), "norm": torch.randn(W, generator=g)}
+    want = O.token_side(x.double(), toks, table.double(), {k: v.double() for k, v in P.items()}, 2, dim, m, eps)
+    gx = (x @ P["gate"].T).to(DEV)
+    gpad = M.side_gate(gx, table.to(DEV), torch.tensor(toks, dtype=torch.int32, device=DEV), 2 * dim, dim, 8)
+    assert gpad.shape == (T, 8) and torch.all(gpad[:, dim:] == 0)
+    r = x.clone().to(DEV)
+    M.resid_norm_step(r, (gpad[:, :dim].cpu() @ P["proj"].T).to(DEV), P["norm"].to(DEV), None, None, eps, torch.float32, m)
+    assert torch.allclose(r.double().cpu(), want, atol=1e-5)
+    z = torch.randn(5, V, generator=g) * 20
+    got = M.scale_softcap_(z.clone().to(DEV), 0.25, 6.0).cpu()
+    assert torch.allclose(got, 6.0 * torch.tanh(z * 0.25 / 6.0), atol=1e-6) and got.abs().max() < 6.0
+    assert torch.allclose(M.scale_softcap_(z.clone().to(DEV), 0.5, 0.0).cpu(), z * 0.5)
+
+
+@pytest.mark.parametrize("layer", [ATT, dict(ATT, mlp=None), dict(ATT, mixer=dict(ATT["mixer"], conv=1, q_temp=None)),
+                                   dict(ATT, mlp=dict(MOE, shared=None, router={"experts": 3, "top": 3}))],
+                         ids=["experts_and_shared", "mixer_alone", "no_filter_no_temperature", "all_experts_no_shared"])
+def test_one_layer_of_each_kind(layer):
+    cfg = make_cfg([layer])
+    W = O.random_weights(cfg, seed=1)
+    toks = tokens(23, cfg["vocab"], 2)
+    want = O.forward(cfg, W, toks)
+    eng = make_engine(cfg, W)
+    close(feed(eng, 1, toks, [len(toks)]), want)
+    close(feed(eng, 2, toks, [3, 1, 2]), want)
+
+
+def test_stream_after_every_layer(stack):
+    W, toks, _ = stack
+    handed = []
+    O.forward(STACK, W, toks, handed)
+    eng = make_engine(STACK, W)
+    eng.model().layer_outputs = []
+    feed(eng, 1, toks, [len(toks)])
+    assert len(handed) == len(eng.model().layer_outputs) == 6          # layers 1 and 2 run twice
+    for got, want in zip(eng.model().layer_outputs, handed):
+        assert torch.allclose(got.double().cpu(), want, atol=2e-4, rtol=1e-4)
+
+
+# ------------------------------------------------------------------------------------------------ cache, state, batches
+def test_prefill_equals_token_by_token_decoding(stack):
+    W, toks, want = stack
+    eng = make_engine(STACK, W)
+    close(feed(eng, 1, toks, [len(toks)]), want)
+    close(feed(eng, 2, toks, [1]), want)
+
+
+@pytest.mark.parametrize("sizes", [[2], [3, 5], [7, 1, 1, 2], [16, 2, 9], [40, 1], [1, 2]])
+def test_prompt_portions(stack, sizes):
+    W, toks, want = stack
+    eng = make_engine(STACK, W)
+    close(feed(eng, 1, toks, sizes), want)
+
+
+def test_unequal_requests_in_one_batch_equal_each_alone():
+    W = O.random_weights(STACK, seed=9)
+    reqs = {u: tokens(n, STACK["vocab"], 10 + u) for u, n in ((1, 19), (2, 3), (3, 31), (4, 8))}
+    want = {u: O.forward(STACK, W, t) for u, t in reqs.items()}
+    eng = make_engine(STACK, W)
+    at = {u: 0 for u in reqs}
+    got = {u: [] for u in reqs}
+    plan = [{1: 5, 3: 2}, {1: 1, 2: 3, 3: 9, 4: 2}, {1: 13, 3: 1, 4: 1}, {3: 1, 4: 5}, {3: 18}]   # 2 is left out, 1 ends
+    for step in plan:
+        uids = list(step)
+        toks = [torch.tensor(reqs[u][at[u]: at[u] + n]) for u, n in step.items()]
+        out = eng.put(uids, toks, logit_positions=[list(range(n)) for n in step.values()]).double().cpu()
+        k = 0
+        for u, n in step.items():
+            got[u].append(out[k: k + n])
+            k, at[u] = k + n, at[u] + n
+    for u in reqs:
+        assert at[u] == len(reqs[u])
+        close(torch.cat(got[u]), want[u])
+
+
+def test_pages_and_state_slots_are_reused():
+    """As many pages as the longest request and its neighbour need, two state slots: every later request gets pages and
+    a slot that an earlier one filled, in another order, and must come out as if alone."""
+    W = O.random_weights(STACK, seed=3)
+    eng = make_engine(STACK, W, blocks=10, block_size=4, max_live=2)
+    for i in range(4):
+        toks = tokens(20 + 3 * i, STACK["vocab"], 20 + i)
+        other = tokens(6, STACK["vocab"], 40 + i)
+        eng.put([100 + i], [torch.tensor(other)])                 # a neighbour that holds the other slot and two pages
+        got = feed(eng, i, toks, [7, 1, 2])
+        close(got, O.forward(STACK, W, toks))
+        eng.flush(i)
+        eng.flush(100 + i)
+        assert eng.free_blocks == 10
+
+
+def test_far_keys_and_bucket_edges_decide_the_logits():
+    """One layer, a table of 6 rows whose entries differ by several units and query / key weights scaled up so that the
+    softmax is peaked: single keys up to 140 positions back (beyond ``far`` = 100) carry most of a query's weight, and
+    a bucket that is one distance off changes the logits; prompt rows, portions cut at page borders and beside them,
+    and decode tokens must all follow the plain evaluation."""
+    layer = dict(ATT, mixer=dict(ATT["mixer"], bias_max=100, scale=1.2), mlp=None)
+    cfg = make_cfg([layer], vocab=31)
+    W = O.random_weights(cfg, seed=21, rel_rows=6)
+    W["l0.mix.rel"] = W["l0.mix.rel"] * 4
+    W["l0.mix.q.norm"] = W["l0.mix.q.norm"] * 3
+    toks = tokens(150, cfg["vocab"], 22)
+    want = O.forward(cfg, W, toks)
+    eng = make_engine(cfg, W, block_size=8, blocks=64, max_tokens=160)
+    close(feed(eng, 1, toks, [len(toks)]), want)
+    close(feed(eng, 2, toks, [95] + [1] * 55), want)
+    close(feed(eng, 3, toks, [64, 37, 3, 2, 40, 4]), want)
+
+
+def test_long_decoding(stack):
+    W, _, _ = stack
+    toks = tokens(150, STACK["vocab"], 6)
+    want = O.forward(STACK, W, toks)
+    eng = make_engine(STACK, W)
+    close(feed(eng, 1, toks, [9] + [1] * 200), want)
+
+
+ODD = [
+    make_cfg([dict(ATT, mixer={"bias_max": 9, "conv": 2, "dim": 5, "heads": 3, "kv_heads": 1, "scale": 1.7, "vdim": 3,
+                               "q_temp": {"coef": 1.0, "every": 1}},
+                   mlp={"expert": {"ff": 7}, "kind": "moe", "router": {"experts": 3, "top": 1}, "shared": {"ff": 3}})],
+             width=10, vocab=17, side=3, mult=1.0, eps=1e-3, logit_scale=1.0, softcap=0.0),
+    make_cfg([dict(ATT, mixer={"bias_max": 1000, "conv": 6, "dim": 33, "heads": 1, "kv_heads": 1, "scale": 0.1,
+                               "vdim": 40, "q_temp": {"coef": 0.05, "every": 64}},
+                   mlp={"expert": {"ff": 64}, "kind": "moe", "router": {"experts": 2, "top": 2}, "shared": None}),
+              dict(ATT, mixer=dict(ATT["mixer"], dim=16, heads=8, kv_heads=8, vdim=4), mlp=None)],
+             width=64, vocab=29, side=0, loop={"start": 0, "stop": 2, "times": 3}),
+    make_cfg([ATT] * 3, width=8, vocab=11, side=1, loop={"start": 2, "stop": 3, "times": 1}, mult=2.0, softcap=1.5),
+    make_cfg([dict(ATT, mlp=None), ATT], width=16, vocab=23, side=16, loop={"start": 1, "stop": 1, "times": 4}),
+]
+
+
+@pytest.mark.parametrize("cfg", ODD, ids=["no_multiples_of_8_one_kv_head_top_1_multiplier_1_no_cap",
+                                          "one_head_long_filter_whole_stack_thrice_no_token_input",
+                                          "same_layer_three_times_loop_of_one_pass", "empty_loop_wide_token_input"])
+def test_other_sizes(cfg):
+    W = O.random_weights(cfg, seed=8, rel_rows=2 + 2 * len(cfg["layers"]))
+    toks = tokens(21, cfg["vocab"], 9)
+    want = O.forward(cfg, W, toks)
+    eng = make_engine(cfg, W, block_size=8)
+    close(feed(eng, 1, toks, [len(toks)]), want)
+    close(feed(eng, 2, toks, [4, 1, 2]), want)
+
+
+def test_configuration_is_read_into_the_layer_specs():
+    from shuffle_exchange_b200.inference.v2.checkpoint.huggingface_engine import PlainModelConfig
+    from shuffle_exchange_b200.inference.v2.model_implementations.ridazen import RidazenPolicy
+    spec = RidazenPolicy(PlainModelConfig(STACK)).spec(PlainModelConfig(STACK))
+    a, b, c, d = spec.layers
+    assert (a.n_heads, a.n_heads_kv, a.key_dim, a.value_dim, a.conv_taps, a.attn_scale) == (4, 2, 8, 12, 3, 0.3)
+    assert (a.q_temp_coef, a.q_temp_every, a.dist_far, a.out_gate, a.qk_norm_weight) == (0.4, 5, 40, True, True)
+    assert (a.ff_kind, a.ff_dim, a.n_experts, a.top_k, a.shared_ff_dim, a.ff_gated, a.ff_activation) == (
+        "moe", 16, 5, 2, 12, False, "relu_sq")
+    assert b.ff_dim == 0 and (c.conv_taps, c.n_heads_kv, c.value_dim) == (2, 4, 8)
+    assert (spec.block_form, spec.residual_mult, spec.token_side_dim, spec.logit_scale, spec.logit_softcap) == (
+        "pre_scaled", 0.4, 6, 0.5, 8.0)
+    assert (spec.loop_start, spec.loop_stop, spec.loop_times) == (1, 3, 2) and len(spec.runs()) == 6
+
+
+def test_bf16_serving_stays_near_the_exact_evaluation(stack):
+    W, toks, want = stack
+    eng = make_engine(STACK, W, dtype=torch.bfloat16)
+    for uid, sizes in ((1, [len(toks)]), (2, [5, 1, 2])):
+        d = feed(eng, uid, toks, sizes) - want
+        err = (d - d.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt() / want.std()
+        # a token whose best experts score nearly alike may be routed otherwise in 16-bit: a few rows may differ
+        assert err.median() < 0.02 and (err > 0.08).sum() <= 3, err
+
+
+# ------------------------------------------------------------------------------------------------ generation
+def _check_greedy(prompt, out, W, cfg):
+    seq = list(prompt)
+    for tok in out:
+        logits = O.forward(cfg, W, seq)[-1]
+        top2 = logits.topk(2).values
+        if top2[0] - top2[1] > 1e-3:                           # a near tie may go either way in 32-bit
+            assert tok == int(logits.argmax())
+        seq.append(tok)
+
+
+def test_greedy_generation_through_the_scheduler():
+    W = O.random_weights(STACK, seed=12)
+    prompts = [tokens(n, STACK["vocab"], 30 + n) for n in (5, 17, 2, 9, 12)]          # five requests, four may be live
+    eng = make_engine(STACK, W, blocks=40, block_size=4, max_live=4, max_tokens=16)
+    got = generate(eng, prompts, max_new_tokens=6, max_batch_tokens=16, max_prompt_portion=7)
+    for p, out in zip(prompts, got):
+        _check_greedy(p, out, W, STACK)
+        assert len(out) == 6
+    assert eng.free_blocks == 40 and eng._state_manager.n_tracked_sequences == 0
+
+
+def test_command_line_generation_from_a_checkpoint_folder(tmp_path):
+    """``config.json`` + ``model.safetensors`` (bf16) on disk, ``bin/sxb_generate`` picks the model class by the
+    configuration, loads the tensors by their checkpoint names and continues two prompts greedily."""
+    import json
+    import os
+    import struct
+    import subprocess
+    import sys
+    W = {k: v.to(torch.bfloat16).float() for k, v in O.random_weights(STACK, seed=14).items()}
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(STACK, f)
+    meta, blobs, off = {}, [], 0
+    for name, t in W.items():
+        b = t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
+        meta[name] = {"dtype": "BF16", "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    header = json.dumps(meta).encode()
+    with open(tmp_path / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(header)) + header + b"".join(blobs))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    prompts = [[5, 17, 3], [9, 9, 1, 2, 3, 4, 5, 6, 7]]
+    cmd = [sys.executable, os.path.join(root, "bin", "sxb_generate"), "--model", str(tmp_path), "--max-new-tokens", "4",
+           "--dtype", "float32"]
+    for p in prompts:
+        cmd += ["--prompt", ",".join(map(str, p))]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(x) for x in r.stdout.splitlines() if x.startswith("{")]
+    assert [x["prompt"] for x in lines] == prompts
+    for p, x in zip(prompts, lines):
+        _check_greedy(p, x["generated"], W, STACK)
+        assert len(x["generated"]) == 4

@@ -143,13 +143,46 @@ qk_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* __restri
   }
 }
 
-// The same append for projections that pass a short causal filter first.  One CTA per token, one warp per head slot;
-// a lane holds channels lane + 32 i of its head (head sizes up to 256).  Every channel of q | k | v is filtered over time
-// (w [C, taps], last tap = current token; earlier inputs from this batch's rows, else from the slot's carried inputs
-// state [slots, taps-1, C], else zero; w null: no filter), q and k heads are divided by their root mean square and
-// multiplied by a weight of d entries that all heads share (null: none), and q by 1 + coef * ln(floor((pos + 1) / every)
-// + 1).  Filter sums, norms and the temperature are fp32.
-template <typename T>
+// The same append for projections that pass a short causal filter first.  One warp per (token, head slot): grid
+// (tokens, ceil(slots / 4)), four warps per CTA.  A lane holds VEC consecutive channels of its head (VEC = head size / 32
+// rounded up to a power of two, head sizes up to 256) and moves them with one access of VEC elements when the head sizes
+// and the row pitch allow.  Every channel of q | k | v is filtered over time (w [C, taps], last tap = current token;
+// earlier inputs from this batch's rows, else from the slot's carried inputs state [slots, taps-1, C], else zero; w null:
+// no filter), q and k heads are divided by their root mean square and multiplied by a weight of d entries that all
+// heads share (null: none), and q by 1 + coef * ln(floor((pos + 1) / every) + 1).  Filter sums, norms and the
+// temperature are fp32.
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) Pack {
+  T v[VEC];
+};
+
+template <typename T, int VEC>
+__device__ __forceinline__ void load_pack(const T* p, float* o, bool vec, int valid) {
+  if (vec) {
+    const Pack<T, VEC> pk = *reinterpret_cast<const Pack<T, VEC>*>(p);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o[i] = to_f32<T>(pk.v[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o[i] = i < valid ? to_f32<T>(p[i]) : 0.f;
+  }
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void store_pack(T* p, const float* o, bool vec, int valid) {
+  if (vec) {
+    Pack<T, VEC> pk;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) pk.v[i] = from_f32<T>(o[i]);
+    *reinterpret_cast<Pack<T, VEC>*>(p) = pk;
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i)
+      if (i < valid) p[i] = from_f32<T>(o[i]);
+  }
+}
+
+template <typename T, int VEC>
 __global__ void __launch_bounds__(128)
 qkv_filter_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ w,
                               const T* __restrict__ state, const int* __restrict__ seq_info,
@@ -157,60 +190,63 @@ qkv_filter_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* 
                               T* __restrict__ kcache, T* __restrict__ vcache, const int* __restrict__ tok_seq,
                               const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks,
                               int block_size, int Hq, int G, int d, int dv, int taps, float eps, int normalize,
-                              float temp_coef, int temp_every) {
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+                              float temp_coef, int temp_every, int vec_ok) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int s = blockIdx.y * 4 + warp;
+  if (s >= Hq + 2 * G) return;
   const int pos = tok_pos[t];
   const int* si = seq_info + 4 * tok_seq[t];
   const int local = t - si[0], seen = si[2];
   const int C = (Hq + G) * d + G * dv;
   const T* st = state ? state + (long long)si[3] * (taps - 1) * C : nullptr;
-  const long long page = tables[(long long)tok_seq[t] * max_blocks + pos / block_size];
-  const long long slot = page * block_size + pos % block_size;
-  const float temp = temp_coef != 0.f ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every + 1)) : 1.f;
-  for (int s = warp; s < Hq + 2 * G; s += nw) {
-    const bool is_v = s >= Hq + G;
-    const int n = is_v ? dv : d;
-    const int col = is_v ? (Hq + G) * d + (s - Hq - G) * dv : s * d;
-    float v[8];
+  const bool is_v = s >= Hq + G;
+  const int n = is_v ? dv : d;
+  const int col = is_v ? (Hq + G) * d + (s - Hq - G) * dv : s * d;
+  const int c0 = lane * VEC;
+  const int valid = min(VEC, n - c0);          // channels of this lane (<= 0: none)
+  const bool vec = vec_ok && valid == VEC;
+  float v[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) v[i] = 0.f;
+  if (valid > 0) {
+    const int ch = col + c0;
+    if (w == nullptr) {
+      load_pack<T, VEC>(qkv + (long long)t * ld + ch, v, vec, valid);
+    } else {
+      for (int j = 0; j < taps; ++j) {
+        const int src = local - j;
+        float u[VEC];
+        if (src >= 0) load_pack<T, VEC>(qkv + (long long)(t - j) * ld + ch, u, vec, valid);
+        else if (seen + src >= 0) load_pack<T, VEC>(st + (long long)(taps - 1 + src) * C + ch, u, vec, valid);
+        else continue;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+          if (i < valid) v[i] += to_f32<T>(w[(long long)(ch + i) * taps + (taps - 1 - j)]) * u[i];
+      }
+    }
+  }
+  float inv = 1.f;
+  const T* hw = nullptr;
+  if (!is_v) {
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int c = lane + 32 * i;
-      v[i] = 0.f;
-      if (c >= n) continue;
-      const int ch = col + c;
-      if (w == nullptr) {
-        v[i] = to_f32<T>(qkv[(long long)t * ld + ch]);
-      } else {
-        float a = 0.f;
-        for (int j = 0; j < taps; ++j) {
-          const int src = local - j;
-          float u = 0.f;
-          if (src >= 0) u = to_f32<T>(qkv[(long long)(t - j) * ld + ch]);
-          else if (seen + src >= 0) u = to_f32<T>(st[(long long)(taps - 1 + src) * C + ch]);
-          a += to_f32<T>(w[(long long)ch * taps + (taps - 1 - j)]) * u;
-        }
-        v[i] = a;
-      }
-      ss += v[i] * v[i];
-    }
-    float inv = 1.f;
-    const T* hw = nullptr;
-    if (!is_v) {
-      ss = warp_sum(ss);
-      if (normalize) inv = 1.f / sqrtf(ss / (float)d + eps);
-      hw = s < Hq ? q_w : k_w;
-      if (s < Hq) inv *= temp;
-    }
+    for (int i = 0; i < VEC; ++i) ss += v[i] * v[i];
+    ss = warp_sum(ss);
+    if (normalize) inv = 1.f / sqrtf(ss / (float)d + eps);
+    hw = s < Hq ? q_w : k_w;
+    if (s < Hq && temp_coef != 0.f) inv *= 1.f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
+  }
+  if (valid <= 0) return;
+  float o[VEC];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int c = lane + 32 * i;
-      if (c >= n) continue;
-      const float o = v[i] * inv * (hw ? to_f32<T>(hw[c]) : 1.f);
-      if (s < Hq) q_out[((long long)t * Hq + s) * d + c] = o;
-      else if (!is_v) kcache[(slot * G + (s - Hq)) * d + c] = from_f32<T>(o);
-      else vcache[(slot * G + (s - Hq - G)) * dv + c] = from_f32<T>(o);
-    }
+  for (int i = 0; i < VEC; ++i) o[i] = v[i] * inv * ((hw && i < valid) ? to_f32<T>(hw[c0 + i]) : 1.f);
+  if (s < Hq) {
+    store_pack<float, VEC>(q_out + ((long long)t * Hq + s) * d + c0, o, vec, valid);
+  } else {
+    const long long page = tables[(long long)tok_seq[t] * max_blocks + pos / block_size];
+    const long long slot = page * block_size + pos % block_size;
+    if (!is_v) store_pack<T, VEC>(kcache + (slot * G + (s - Hq)) * d + c0, o, vec, valid);
+    else store_pack<T, VEC>(vcache + (slot * G + (s - Hq - G)) * dv + c0, o, vec, valid);
   }
 }
 
@@ -1419,11 +1455,25 @@ SXB_API int sxb_qkv_filter_norm_append(const void* qkv, long long ld, const void
   if (n_tokens <= 0) return SXB_OK;
   if (d > 256 || dv > 256 || taps < 1 || taps > kMaxTaps || temp_every < 1) return SXB_ERR_UNSUPPORTED;
   if (conv_w != nullptr && taps > 1 && state == nullptr) return SXB_ERR_BAD_ARG;
-  SEQMIX_DISPATCH(dtype, (qkv_filter_norm_append_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(
-                             (const T*)qkv, ld, (const T*)conv_w, (const T*)state, (const int*)seq_info, (const T*)q_w,
-                             (const T*)k_w, (float*)q_out, (T*)kcache, (T*)vcache, (const int*)tok_seq,
-                             (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, taps, eps,
-                             normalize, temp_coef, temp_every)));
+  const int widest = std::max(d, dv);
+  const int vecw = widest <= 32 ? 1 : (widest <= 64 ? 2 : (widest <= 128 ? 4 : 8));
+  // one access per lane needs every head to start on a multiple of the lane's channels, in the rows and the caches
+  const int vec_ok = d % vecw == 0 && dv % vecw == 0 && ld % vecw == 0 &&
+                     ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(state) |
+                       reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(kcache) |
+                       reinterpret_cast<uintptr_t>(vcache)) & 31) == 0;
+  const dim3 grid(n_tokens, (Hq + 2 * G + 3) / 4);
+#define FILTER_APPEND(VEC)                                                                                             \
+  SEQMIX_DISPATCH(dtype, (qkv_filter_norm_append_kernel<T, VEC><<<grid, 128, 0, (cudaStream_t)stream>>>(               \
+                             (const T*)qkv, ld, (const T*)conv_w, (const T*)state, (const int*)seq_info, (const T*)q_w, \
+                             (const T*)k_w, (float*)q_out, (T*)kcache, (T*)vcache, (const int*)tok_seq,                \
+                             (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, taps, eps, \
+                             normalize, temp_coef, temp_every, vec_ok)))
+  if (vecw == 1) FILTER_APPEND(1);
+  else if (vecw == 2) FILTER_APPEND(2);
+  else if (vecw == 4) FILTER_APPEND(4);
+  else FILTER_APPEND(8);
+#undef FILTER_APPEND
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }

@@ -3,7 +3,9 @@ through ``InferenceEngineV2.put`` with random weights, plus device times of the 
 counterparts against the memory roofline.  ``bench.py --serve`` prints the result as one JSON object.  With
 ``--serve-model kekopel`` the pair is a Kekopel stack (latent attention with a sliding window, matrix-memory LSTM,
 post-scaled layers, dense and expert feed-forwards) next to the Fomalix stack of equal size, and the kernel table sets
-every Kekopel kernel beside the Fomalix kernel that does the like job.
+every Kekopel kernel beside the Fomalix kernel that does the like job.  With ``--serve-model ridazen`` the pair is a
+Ridazen stack (attention with filtered projections, distance-bucket bias and output gate, squared-ReLU experts with a
+shared expert, per-layer token input) next to a Fomalix stack of attention layers only at equal size.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up forwards, a buffer larger than L2 is rewritten between timed
 forwards.  Prefill: one request of ``prefill`` tokens in one forward.  Decode: ``batch`` requests with ``context`` tokens
@@ -31,8 +33,7 @@ VOCAB = 32000
 CHUNK = 4096          # the prompt and the decode context fall into one chunk: attention work equals full causal
 
 
-def hybrid_config(z: Dict) -> Dict:
-    kinds = ["delta", "mamba2", "attention"]
+def hybrid_config(z: Dict, kinds=("delta", "mamba2", "attention")) -> Dict:
     mixers = {
         "delta": {"conv": 4, "dim": z["head"], "heads": z["heads"], "kv_heads": z["heads"], "vdim": z["head"]},
         "mamba2": {"conv": 4, "groups": 1, "heads": z["ssd_heads"], "norm_groups": 1, "state": z["state"],
@@ -40,8 +41,8 @@ def hybrid_config(z: Dict) -> Dict:
         "attention": {"dim": z["head"], "heads": z["heads"], "kv_heads": z["kv_heads"], "mask": {"size": CHUNK},
                       "scale": z["head"] ** -0.5, "vdim": z["head"]},
     }
-    layers = [{"type": kinds[i % 3], "mixer": mixers[kinds[i % 3]], "mlp": {"ff": z["ff"], "kind": "dense"}}
-              for i in range(z["layers"])]
+    layers = [{"type": kinds[i % len(kinds)], "mixer": mixers[kinds[i % len(kinds)]],
+               "mlp": {"ff": z["ff"], "kind": "dense"}} for i in range(z["layers"])]
     return {"architecture": "Fomalix", "embedding": {"scale": 1.0}, "layers": layers, "norm": {"eps": 1e-5},
             "vocab": VOCAB, "width": z["width"]}
 
@@ -500,6 +501,200 @@ def kekopel_kernel_table(z: Dict, prefill: int, batch: int, context: int, timer,
     return rows
 
 
+# ------------------------------------------------------------------------------------------------ Ridazen beside Fomalix
+RIDAZEN = dict(taps=4, rows=32, far=1024, every=64, coef=0.1, experts=8, top=2, side=64)
+
+
+def ridazen_config(z: Dict) -> Dict:
+    mixer = {"bias_max": RIDAZEN["far"], "conv": RIDAZEN["taps"], "dim": z["head"], "heads": z["heads"],
+             "kv_heads": z["kv_heads"], "q_temp": {"coef": RIDAZEN["coef"], "every": RIDAZEN["every"]},
+             "scale": z["head"] ** -0.5, "vdim": z["head"]}
+    mlp = {"expert": {"ff": z["ff"] // 4}, "kind": "moe", "router": {"experts": RIDAZEN["experts"], "top": RIDAZEN["top"]},
+           "shared": {"ff": z["ff"] // 4}}
+    return {"architecture": "Ridazen", "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp}] * z["layers"],
+            "logit_scale": 0.5, "logit_softcap": 30.0, "loop": None, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "token_side": {"dim": RIDAZEN["side"]}, "vocab": VOCAB, "width": z["width"]}
+
+
+def ridazen_weights(cfg: Dict, device) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(0)
+    W, bf = cfg["width"], torch.bfloat16
+
+    def mat(o, i):
+        return (torch.randn(o, i, generator=g, device=device) / math.sqrt(i)).to(bf)
+
+    def vec(n, lo=0.5, hi=1.5):
+        return (torch.rand(n, generator=g, device=device) * (hi - lo) + lo).to(bf)
+
+    ds = cfg["token_side"]["dim"]
+    out = {"embed": mat(cfg["vocab"], W), "head": mat(cfg["vocab"], W), "final.norm": vec(W),
+           "side.embed": mat(cfg["vocab"], len(cfg["layers"]) * ds)}
+    for i, L in enumerate(cfg["layers"]):
+        m, mlp, p = L["mixer"], L["mlp"], f"l{i}."
+        H, G, d, dv, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+        out[p + "norm1"], out[p + "norm2"] = vec(W), vec(W)
+        for n, o in (("q", H * d), ("k", G * d), ("v", G * dv)):
+            out[p + "mix." + n], out[p + "mix." + n + ".conv"] = mat(o, W), vec(o * taps, -0.5, 0.5).view(o, taps)
+        out[p + "mix.q.norm"], out[p + "mix.k.norm"] = vec(d), vec(d)
+        out[p + "mix.rel"] = vec(RIDAZEN["rows"] * H, -1, 1).view(RIDAZEN["rows"], H)
+        out[p + "mix.g"], out[p + "mix.o"] = mat(H * dv, W), mat(W, H * dv)
+        Fe, Fs, E = mlp["expert"]["ff"], mlp["shared"]["ff"], mlp["router"]["experts"]
+        out[p + "mlp.router"], out[p + "mlp.router.b"] = mat(E, W), vec(E, -0.5, 0.5)
+        for e in range(E):
+            out[p + f"mlp.e{e}.up"], out[p + f"mlp.e{e}.down"] = mat(Fe, W), mat(W, Fe)
+        out[p + "mlp.shared.up"], out[p + "mlp.shared.down"] = mat(Fs, W), mat(W, Fs)
+        out[p + "mlp.shared.sg"] = mat(1, W)
+        out[p + "side.gate"], out[p + "side.proj"], out[p + "side.norm"] = mat(ds, W), mat(W, ds), vec(W)
+    return out
+
+
+def build_ridazen(z: Dict, max_tokens: int, max_seqs: int, pages: int):
+    cfg = ridazen_config(z)
+    return build_engine_from_state_dict(cfg, ridazen_weights(cfg, "cuda"), _engine_config(max_tokens, max_seqs, pages),
+                                        dtype=torch.bfloat16)
+
+
+def build_attention_stack(z: Dict, max_tokens: int, max_seqs: int, pages: int):
+    """The Fomalix stack with attention layers only (per-head keys, sink, dense gated feed-forward)."""
+    cfg = hybrid_config(z, kinds=("attention",))
+    return build_engine_from_state_dict(cfg, hybrid_weights(cfg, "cuda"), _engine_config(max_tokens, max_seqs, pages),
+                                        dtype=torch.bfloat16)
+
+
+def ridazen_kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs: float,
+                         peak_tflops: Dict[str, float]) -> List[Dict]:
+    """Every Ridazen kernel beside the kernel of the Fomalix (or Kekopel) stack that does the like job (``like``), at
+    prefill (one request) and decode (``batch`` requests) shapes: device time, algorithmic bytes and FLOPs, fraction
+    of the roofline (the larger of bytes / copy bandwidth and FLOPs / the peak of the unit the products run on)."""
+    from ...moe import fused_ep
+    from ...ops import functional as F
+    from ...ops import moe_ops
+    from .kernels import mixer_ops as M
+    from .modules.implementations import DSFilteredBiasAttention
+    from .ragged.ragged_wrapper import RaggedBatchWrapper
+    dev, bf = "cuda", torch.bfloat16
+    W, H, G, d, ff = z["width"], z["heads"], z["kv_heads"], z["head"], z["ff"]
+    taps, ds = RIDAZEN["taps"], RIDAZEN["side"]
+    rows: List[Dict] = []
+
+    def add(name, like, phase, fn, nbytes, flops=0.0, pipe=None):
+        ms = timer(fn, 5, 3)
+        ideal_ms = nbytes / hbm_gbs / 1e6
+        if pipe is not None:
+            ideal_ms = max(ideal_ms, flops / peak_tflops[pipe] / 1e9)
+        rows.append({"kernel": name, "like": like, "phase": phase, "ms": round(ms, 4),
+                     "GB_s": round(nbytes / ms / 1e6, 1), "GFLOP_s": round(flops / ms / 1e6, 1), "pipe": pipe or "memory",
+                     "of_roofline": round(ideal_ms / ms, 3)})
+
+    for phase, T, n_seq, seen in (("prefill", prefill, 1, 0), ("decode", batch, batch, context)):
+        per = T // n_seq
+        tot = seen + per
+        n_pages_seq = (tot + 63) // 64
+        t2s = torch.arange(n_seq, device=dev, dtype=torch.int32).repeat_interleave(per)
+        pos = (torch.arange(per, device=dev, dtype=torch.int32) + seen).repeat(n_seq)
+        tables = torch.arange(n_seq * n_pages_seq, device=dev, dtype=torch.int32).view(n_seq, n_pages_seq)
+        info = torch.tensor([[i * per, per, seen, i] for i in range(n_seq)], dtype=torch.int32, device=dev)
+        x32 = torch.randn(T, W, device=dev)
+        y = torch.randn(T, W, device=dev).to(bf)
+        wv = torch.ones(W, device=dev, dtype=bf)
+        add("resid_norm_step (scaled add + pre-norm)", None, phase,
+            lambda: M.resid_norm_step(x32, y, None, None, wv, 1e-5, bf, 0.5), T * W * (4 + 4 + 2 + 2))
+        add("resid_norm_step (scaled add + 16-bit copy)", None, phase,
+            lambda: M.resid_norm_step(x32, y, None, None, None, 1e-5, bf, 0.5, copy_out=True), T * W * (4 + 4 + 2 + 2))
+        add("resid_norm_step (post-norm + add + pre-norm)", "resid_norm_step (scaled add + pre-norm)", phase,
+            lambda: M.resid_norm_step(x32, y, wv, None, wv, 1e-5, bf), T * W * (4 + 4 + 2 + 2))
+        # projections -> filter -> norm -> cache
+        C = (H + 2 * G) * d
+        proj = torch.randn(T, C + H * d, device=dev).to(bf)
+        cw = (torch.randn(C, taps, device=dev) * 0.3).to(bf)
+        cst = torch.zeros(n_seq, taps - 1, C, device=dev, dtype=bf)
+        nq = torch.ones(d, device=dev, dtype=bf)
+        kc = torch.randn(n_seq * n_pages_seq, 64, G, d, device=dev).to(bf)
+        vc = torch.randn(n_seq * n_pages_seq, 64, G, d, device=dev).to(bf)
+        add("qkv_filter_norm_append + state update", None, phase,
+            lambda: (M.qkv_filter_norm_append(proj, cw, cst, info, nq, nq, kc, vc, t2s, pos, tables, H, G, d, d, 1e-5,
+                                              True, RIDAZEN["coef"], RIDAZEN["every"]),
+                     M.conv_state_update(proj[:, :C], cst, info)),
+            T * (C * 2 + H * d * 4 + 2 * G * d * 2) + n_seq * (taps - 1) * C * 2 * 2)
+        qkv = torch.randn(T, C, device=dev).to(bf)
+        bias = torch.zeros(C, device=dev, dtype=bf)
+        add("qk_norm_append", "qkv_filter_norm_append + state update", phase,
+            lambda: M.qk_norm_append(qkv, bias, kc, vc, t2s, pos, tables, H, G, d, d, 1e-5, True),
+            T * (C * 2 + H * d * 4 + 2 * G * d * 2))
+        wrap = RaggedBatchWrapper(max(T, 64), n_seq, n_pages_seq, device=dev)
+
+        class _Seq:
+            def __init__(self, i):
+                self.seen_tokens, self._b = seen, tables[i].cpu()
+
+            def kv_blocks(self):
+                return self._b
+        for i in range(n_seq):
+            wrap.insert_sequence(_Seq(i), torch.zeros(per, dtype=torch.int32), do_checks=False)
+        wrap.finalize()
+        atoms, n_long = wrap.atoms(), wrap.atoms_longer_than(M.SHORT_ATOM)
+        q32 = torch.randn(T, H, d, device=dev)
+        table = torch.randn(RIDAZEN["rows"], H, device=dev)
+        dist = DSFilteredBiasAttention.expand_distance_bias(table, RIDAZEN["far"])
+        gate = proj[:, C:]
+        keys_per_q = (per + 1) / 2 if phase == "prefill" else tot
+        kv_bytes = n_seq * tot * 2 * G * d * 2
+        fl = 4.0 * T * H * d * keys_per_q
+        add("sink_attention (causal, distance bias, output gate)", None, phase,
+            lambda: M.sink_attention(q32, kc, vc, None, t2s, pos, tables, d ** -0.5, 0, bf, atoms, n_long, dist_bias=dist,
+                                     gate=gate), kv_bytes + T * H * d * 8, fl, "fp32")
+        sink = torch.zeros(H, device=dev)
+        add("sink_attention (causal, sink)", "sink_attention (causal, distance bias, output gate)", phase,
+            lambda: M.sink_attention(q32, kc, vc, sink, t2s, pos, tables, d ** -0.5, 0, bf, atoms, n_long),
+            kv_bytes + T * H * d * 6, fl, "fp32")
+        # per-layer token input and logits
+        dsp = (ds + 7) // 8 * 8
+        gx = torch.randn(T, dsp, device=dev).to(bf)
+        side = torch.randn(VOCAB, 6 * ds, device=dev).to(bf)
+        ids = torch.randint(0, VOCAB, (T,), device=dev, dtype=torch.int32)
+        add("side_gate", None, phase, lambda: M.side_gate(gx, side, ids, 2 * ds, ds, dsp), T * ds * 6)
+        hg = torch.randn(T, 2 * dsp, device=dev).to(bf)
+        add("gated_act_rows", "side_gate", phase, lambda: M.gated_act_rows(hg, "gelu"), T * dsp * 6)
+        # feed-forward
+        E, K, Fe = RIDAZEN["experts"], RIDAZEN["top"], ff // 4
+        hu = torch.randn(T, Fe, device=dev).to(bf)
+        add("bias_act_rows (squared relu, shared expert)", None, phase, lambda: M.bias_act_rows(hu, None, "relu_sq"),
+            T * Fe * 4)
+        hgu = torch.randn(T, 2 * Fe, device=dev).to(bf)
+        add("gated_act", "bias_act_rows (squared relu, shared expert)", phase, lambda: F.gated_act(hgu, "gelu"), T * Fe * 6)
+        acc = torch.randn(T, W, device=dev).to(bf)
+        sg = torch.randn(T, E + 1, device=dev)
+        add("row_gate_add (shared expert into the experts' sum)", None, phase,
+            lambda: M.row_gate_add_(acc, y, sg[:, E]), T * W * 6)
+        add("bias_act_rows (same rows)", "row_gate_add (shared expert into the experts' sum)", phase,
+            lambda: M.bias_act_rows(acc, wv, "identity"), T * W * 4)
+        logits = torch.randn(T, E, device=dev)
+        xe = torch.randn(T, W, device=dev).to(bf)
+        w1 = (torch.randn(E, Fe, W, device=dev) / math.sqrt(W)).to(bf)
+        w1g = (torch.randn(E, 2 * Fe, W, device=dev) / math.sqrt(W)).to(bf)
+        w2 = (torch.randn(E, W, Fe, device=dev) / math.sqrt(Fe)).to(bf)
+
+        def experts(w_up, act, renorm):
+            s_, a_, o_, c_ = moe_ops.top_k_gating(logits, K, renormalize=renorm, score_function="softmax")
+            return fused_ep.grouped_experts_inference(xe, s_, a_, o_, c_, w_up, w2, act, K)
+        add("experts: top-k softmax, squared-relu experts, grouped GEMMs, weighted sum", None, phase,
+            lambda: experts(w1, lambda t: M.bias_act_rows(t, None, "relu_sq"), True),
+            E * 2 * Fe * W * 2 + T * W * 2 * (1 + 2 * K + 1) + T * K * 2 * Fe * 2, 2.0 * T * K * 2 * Fe * W, "bf16")
+        add("experts: softmax gating, gated experts, grouped GEMMs, weighted sum",
+            "experts: top-k softmax, squared-relu experts, grouped GEMMs, weighted sum", phase,
+            lambda: experts(w1g, F.swiglu, False),
+            E * 3 * Fe * W * 2 + T * W * 2 * (1 + 2 * K + 1) + T * K * 3 * Fe * 2, 2.0 * T * K * 3 * Fe * W, "bf16")
+        lg = torch.randn(n_seq, VOCAB, device=dev)
+        add("scale_softcap (logits)", None, phase, lambda: M.scale_softcap_(lg, 0.5, 30.0), n_seq * VOCAB * 8)
+    by_name = {(r_["kernel"], r_["phase"]): r_ for r_ in rows}
+    for r_ in rows:                      # distance from the roofline relative to the like kernel's
+        if r_["like"]:
+            mine = by_name[(r_["like"], r_["phase"])]
+            mine["like_of_roofline"] = r_["of_roofline"]
+            mine["like_kernel"] = r_["kernel"]
+    return rows
+
+
 def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, warmup: int, kernels: bool = True,
         chunk: int = 0, model: str = "fomalix") -> Dict:
     global CHUNK, WINDOW
@@ -533,6 +728,19 @@ def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, wa
                      "fomalix": engine_throughput(build_hybrid, z, prefill, batch, context, steps, warmup, timer)}
             if kernels:
                 entry["kernels"] = kekopel_kernel_table(z, prefill, batch, context, timer, hbm, peak_tflops)
+            out["sizes"][name] = entry
+        return out
+    if model == "ridazen":
+        out["metric"] = "serving tokens/s, Ridazen vs a Fomalix stack of attention layers of equal size"
+        out["ridazen"] = RIDAZEN
+        for name in sizes:
+            z = SIZES[name]
+            entry = {"config": z,
+                     "ridazen": engine_throughput(build_ridazen, z, prefill, batch, context, steps, warmup, timer),
+                     "fomalix_attention": engine_throughput(build_attention_stack, z, prefill, batch, context, steps,
+                                                            warmup, timer)}
+            if kernels:
+                entry["kernels"] = ridazen_kernel_table(z, prefill, batch, context, timer, hbm, peak_tflops)
             out["sizes"][name] = entry
         return out
     for name in sizes:

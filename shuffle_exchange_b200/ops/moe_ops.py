@@ -69,6 +69,13 @@ def _scatter_fwd(x, assign, offsets, counts):
     slots = torch.empty(T, K, dtype=torch.int32, device=x.device)
     if x.is_cuda:
         x = x.contiguous()
+        if (H * x.element_size()) % 16 and x.dtype in (torch.bfloat16, torch.float32):
+            # rows that are not whole 16-byte words: the element-wise form of the copy, with unit weights
+            ones = torch.ones(T, K, dtype=torch.float32, device=x.device)
+            _lib.call("sxb_moe_scatter_scaled", x.data_ptr(), ones.data_ptr(), moe_in.data_ptr(), assign.data_ptr(),
+                      offsets.data_ptr(), counts.data_ptr(), cumsum.data_ptr(), slots.data_ptr(), T, E, K, H,
+                      _lib.dtype_code(x.dtype), _lib.stream_ptr())
+            return moe_in, cumsum, slots
         _lib.call("sxb_moe_scatter", x.data_ptr(), moe_in.data_ptr(), assign.data_ptr(), offsets.data_ptr(),
                   counts.data_ptr(), cumsum.data_ptr(), slots.data_ptr(), T, E, K, H, x.element_size(), _lib.stream_ptr())
         return moe_in, cumsum, slots

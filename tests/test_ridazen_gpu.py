@@ -30,7 +30,7 @@ def test_prompts_on_the_tiled_kernel_and_experts_on_the_grouped_gemm_path():
     W = O.random_weights(cfg, seed=31)
     toks = tokens(150, cfg["vocab"], 32)
     want = O.forward(cfg, W, toks)
-    eng = make_engine(cfg, W, dtype=torch.bfloat16, max_tokens=256)
+    eng = make_engine(cfg, W, dtype=torch.bfloat16, max_tokens=256, blocks=128)
     for sizes in ([len(toks)], [70, 1, 33, 1, 1]):
         d = feed(eng, len(sizes), toks, sizes) - want
         err = (d - d.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt() / want.std()

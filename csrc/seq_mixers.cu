@@ -182,7 +182,10 @@ __device__ __forceinline__ void store_pack(T* p, const float* o, bool vec, int v
   }
 }
 
-template <typename T, int VEC>
+// TAPS > 0 (filters of 2 to 4 taps): a warp walks `rows_per_warp` consecutive batch rows with the filter's weights and
+// the last TAPS-1 inputs in registers; the inputs are fetched by the rule above at the warp's first row and at a
+// sequence's first row in the batch, and shifted otherwise.  TAPS == 0: any number of taps (or none), one row per warp.
+template <typename T, int VEC, int TAPS>
 __global__ void __launch_bounds__(128)
 qkv_filter_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ w,
                               const T* __restrict__ state, const int* __restrict__ seq_info,
@@ -190,63 +193,99 @@ qkv_filter_norm_append_kernel(const T* __restrict__ qkv, long long ld, const T* 
                               T* __restrict__ kcache, T* __restrict__ vcache, const int* __restrict__ tok_seq,
                               const int* __restrict__ tok_pos, const int* __restrict__ tables, int max_blocks,
                               int block_size, int Hq, int G, int d, int dv, int taps, float eps, int normalize,
-                              float temp_coef, int temp_every, int vec_ok) {
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+                              float temp_coef, int temp_every, int vec_ok, int n_tokens, int rows_per_warp) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int s = blockIdx.y * 4 + warp;
   if (s >= Hq + 2 * G) return;
-  const int pos = tok_pos[t];
-  const int* si = seq_info + 4 * tok_seq[t];
-  const int local = t - si[0], seen = si[2];
   const int C = (Hq + G) * d + G * dv;
-  const T* st = state ? state + (long long)si[3] * (taps - 1) * C : nullptr;
   const bool is_v = s >= Hq + G;
   const int n = is_v ? dv : d;
   const int col = is_v ? (Hq + G) * d + (s - Hq - G) * dv : s * d;
   const int c0 = lane * VEC;
   const int valid = min(VEC, n - c0);          // channels of this lane (<= 0: none)
   const bool vec = vec_ok && valid == VEC;
-  float v[VEC];
+  const int ch = col + c0;
+  const T* hw = is_v ? nullptr : (s < Hq ? q_w : k_w);
+  float gain[VEC];
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) v[i] = 0.f;
-  if (valid > 0) {
-    const int ch = col + c0;
-    if (w == nullptr) {
-      load_pack<T, VEC>(qkv + (long long)t * ld + ch, v, vec, valid);
-    } else {
-      for (int j = 0; j < taps; ++j) {
-        const int src = local - j;
-        float u[VEC];
-        if (src >= 0) load_pack<T, VEC>(qkv + (long long)(t - j) * ld + ch, u, vec, valid);
-        else if (seen + src >= 0) load_pack<T, VEC>(st + (long long)(taps - 1 + src) * C + ch, u, vec, valid);
-        else continue;
+  for (int i = 0; i < VEC; ++i) gain[i] = (hw && i < valid) ? to_f32<T>(hw[c0 + i]) : 1.f;
+  constexpr int NT = TAPS > 0 ? TAPS : 1;
+  float wt[VEC][NT], hist[NT][VEC];
+  if (TAPS > 0) {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i)
-          if (i < valid) v[i] += to_f32<T>(w[(long long)(ch + i) * taps + (taps - 1 - j)]) * u[i];
+    for (int i = 0; i < VEC; ++i)
+#pragma unroll
+      for (int j = 0; j < NT; ++j) wt[i][j] = i < valid ? to_f32<T>(w[(long long)(ch + i) * NT + j]) : 0.f;
+  }
+  const int t0 = blockIdx.x * rows_per_warp, t1 = min(t0 + rows_per_warp, n_tokens);
+  for (int t = t0; t < t1; ++t) {
+    const int pos = tok_pos[t];
+    const int* si = seq_info + 4 * tok_seq[t];
+    const int local = t - si[0], seen = si[2];
+    const T* st = state ? state + (long long)si[3] * (taps - 1) * C : nullptr;
+    float v[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) v[i] = 0.f;
+    if (valid > 0) {
+      if (TAPS > 0) {
+        if (t == t0 || local == 0) {
+#pragma unroll
+          for (int j = 1; j < NT; ++j) {
+            const int src = local - j;
+            if (src >= 0) load_pack<T, VEC>(qkv + (long long)(t - j) * ld + ch, hist[j], vec, valid);
+            else if (seen + src >= 0) load_pack<T, VEC>(st + (long long)(NT - 1 + src) * C + ch, hist[j], vec, valid);
+            else {
+#pragma unroll
+              for (int i = 0; i < VEC; ++i) hist[j][i] = 0.f;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = NT - 1; j >= 1; --j)
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) hist[j][i] = hist[j - 1][i];
+        }
+        load_pack<T, VEC>(qkv + (long long)t * ld + ch, hist[0], vec, valid);
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) v[i] += wt[i][NT - 1 - j] * hist[j][i];
+      } else if (w == nullptr) {
+        load_pack<T, VEC>(qkv + (long long)t * ld + ch, v, vec, valid);
+      } else {
+        for (int j = 0; j < taps; ++j) {
+          const int src = local - j;
+          float u[VEC];
+          if (src >= 0) load_pack<T, VEC>(qkv + (long long)(t - j) * ld + ch, u, vec, valid);
+          else if (seen + src >= 0) load_pack<T, VEC>(st + (long long)(taps - 1 + src) * C + ch, u, vec, valid);
+          else continue;
+#pragma unroll
+          for (int i = 0; i < VEC; ++i)
+            if (i < valid) v[i] += to_f32<T>(w[(long long)(ch + i) * taps + (taps - 1 - j)]) * u[i];
+        }
       }
     }
-  }
-  float inv = 1.f;
-  const T* hw = nullptr;
-  if (!is_v) {
-    float ss = 0.f;
+    float inv = 1.f;
+    if (!is_v) {
+      float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) ss += v[i] * v[i];
-    ss = warp_sum(ss);
-    if (normalize) inv = 1.f / sqrtf(ss / (float)d + eps);
-    hw = s < Hq ? q_w : k_w;
-    if (s < Hq && temp_coef != 0.f) inv *= 1.f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
-  }
-  if (valid <= 0) return;
-  float o[VEC];
+      for (int i = 0; i < VEC; ++i) ss += v[i] * v[i];
+      ss = warp_sum(ss);
+      if (normalize) inv = 1.f / sqrtf(ss / (float)d + eps);
+      if (s < Hq && temp_coef != 0.f) inv *= 1.f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
+    }
+    if (valid <= 0) continue;
+    float o[VEC];
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) o[i] = v[i] * inv * ((hw && i < valid) ? to_f32<T>(hw[c0 + i]) : 1.f);
-  if (s < Hq) {
-    store_pack<float, VEC>(q_out + ((long long)t * Hq + s) * d + c0, o, vec, valid);
-  } else {
-    const long long page = tables[(long long)tok_seq[t] * max_blocks + pos / block_size];
-    const long long slot = page * block_size + pos % block_size;
-    if (!is_v) store_pack<T, VEC>(kcache + (slot * G + (s - Hq)) * d + c0, o, vec, valid);
-    else store_pack<T, VEC>(vcache + (slot * G + (s - Hq - G)) * dv + c0, o, vec, valid);
+    for (int i = 0; i < VEC; ++i) o[i] = v[i] * inv * gain[i];
+    if (s < Hq) {
+      store_pack<float, VEC>(q_out + ((long long)t * Hq + s) * d + c0, o, vec, valid);
+    } else {
+      const long long page = tables[(long long)tok_seq[t] * max_blocks + pos / block_size];
+      const long long slot = page * block_size + pos % block_size;
+      if (!is_v) store_pack<T, VEC>(kcache + (slot * G + (s - Hq)) * d + c0, o, vec, valid);
+      else store_pack<T, VEC>(vcache + (slot * G + (s - Hq - G)) * dv + c0, o, vec, valid);
+    }
   }
 }
 
@@ -1462,17 +1501,29 @@ SXB_API int sxb_qkv_filter_norm_append(const void* qkv, long long ld, const void
                      ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(state) |
                        reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(kcache) |
                        reinterpret_cast<uintptr_t>(vcache)) & 31) == 0;
-  const dim3 grid(n_tokens, (Hq + 2 * G + 3) / 4);
-#define FILTER_APPEND(VEC)                                                                                             \
-  SEQMIX_DISPATCH(dtype, (qkv_filter_norm_append_kernel<T, VEC><<<grid, 128, 0, (cudaStream_t)stream>>>(               \
+  // prompt batches: a warp walks 8 rows (filters of 2 to 4 taps); few rows: one row per warp spreads them over more CTAs
+  const int ktaps = (conv_w != nullptr && taps >= 2 && taps <= 4) ? taps : 0;
+  const int rpw = (ktaps > 0 && n_tokens >= 1024) ? 8 : 1;
+  const dim3 grid((n_tokens + rpw - 1) / rpw, (Hq + 2 * G + 3) / 4);
+  if (conv_w == nullptr) taps = 1;
+#define FILTER_APPEND_T(VEC, TAPS)                                                                                     \
+  SEQMIX_DISPATCH(dtype, (qkv_filter_norm_append_kernel<T, VEC, TAPS><<<grid, 128, 0, (cudaStream_t)stream>>>(         \
                              (const T*)qkv, ld, (const T*)conv_w, (const T*)state, (const int*)seq_info, (const T*)q_w, \
                              (const T*)k_w, (float*)q_out, (T*)kcache, (T*)vcache, (const int*)tok_seq,                \
                              (const int*)tok_pos, (const int*)tables, max_blocks, block_size, Hq, G, d, dv, taps, eps, \
-                             normalize, temp_coef, temp_every, vec_ok)))
+                             normalize, temp_coef, temp_every, vec_ok, n_tokens, rpw)))
+#define FILTER_APPEND(VEC)                 \
+  do {                                     \
+    if (ktaps == 2) FILTER_APPEND_T(VEC, 2);      \
+    else if (ktaps == 3) FILTER_APPEND_T(VEC, 3); \
+    else if (ktaps == 4) FILTER_APPEND_T(VEC, 4); \
+    else FILTER_APPEND_T(VEC, 0);                 \
+  } while (0)
   if (vecw == 1) FILTER_APPEND(1);
   else if (vecw == 2) FILTER_APPEND(2);
   else if (vecw == 4) FILTER_APPEND(4);
   else FILTER_APPEND(8);
+#undef FILTER_APPEND_T
 #undef FILTER_APPEND
   SXB_CHECK_LAUNCH();
   return SXB_OK;

@@ -110,7 +110,11 @@ class RidazenPolicy(InferenceV2Policy):
             m = p + "mix."
             lw["norm1"] = get(p + "norm1")
             lw["w_in"] = pad_rows(cat([m + "q", m + "k", m + "v", m + "g"]))
-            lw["conv_w"] = cat([m + "q.conv", m + "k.conv", m + "v.conv"]) if L.conv_taps > 1 else None
+            # a filter of one tap is a scale per channel: it is applied whenever the checkpoint has the tensors
+            has_filter = L.conv_taps > 1 or (m + "q.conv") in raw
+            lw["conv_w"] = cat([m + "q.conv", m + "k.conv", m + "v.conv"]) if has_filter else None
+            if has_filter and lw["conv_w"].shape[1] != L.conv_taps:
+                raise ValueError(f"{m}*.conv have {lw['conv_w'].shape[1]} taps, the configuration says {L.conv_taps}")
             lw["q_norm"], lw["k_norm"] = get(m + "q.norm"), get(m + "k.norm")
             lw["dist_bias"] = (DSFilteredBiasAttention.expand_distance_bias(get(m + "rel", f32), L.dist_far)
                                if L.dist_rows > 0 else None)

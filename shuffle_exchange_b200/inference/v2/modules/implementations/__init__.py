@@ -841,12 +841,12 @@ class DSFilteredBiasAttention(DSSelfAttentionBase):
         keys, values = kv_cache
         C = self.filtered_channels
         t2s, pos, tables, info = batch.token_to_seq(), batch.token_positions(), batch.block_tables(), batch.seq_info()
-        conv_w = weights.conv_w if c.qkv_conv_taps > 1 else None
+        conv_w = getattr(weights, "conv_w", None)          # one tap: a scale per channel, nothing carried
         q = M.qkv_filter_norm_append(projected, conv_w, conv_state, info, weights.q_norm if c.qk_norm_weight else None,
                                      weights.k_norm if c.qk_norm_weight else None, keys, values, t2s, pos, tables,
                                      c.n_heads_q, c.n_heads_kv, c.head_size, dv, c.qk_norm_eps, True, c.q_temp_coef,
                                      c.q_temp_every)
-        if conv_w is not None:
+        if conv_w is not None and conv_w.shape[1] > 1:
             M.conv_state_update(projected[:, :C], conv_state, info)
         mt = MaskingType(c.masking_type)
         chunk = int(c.masking_args["size"]) if mt == MaskingType.chunked else 0

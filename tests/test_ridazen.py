@@ -293,6 +293,24 @@ def test_one_layer_of_each_kind(layer):
     close(feed(eng, 2, toks, [3, 1, 2]), want)
 
 
+def test_a_filter_of_one_tap_is_a_scale_per_channel():
+    """``conv`` = 1 with filter tensors in the checkpoint: every projected channel is multiplied by its one weight and
+    nothing is carried between calls."""
+    cfg = make_cfg([dict(ATT, mixer=dict(ATT["mixer"], conv=1))] * 2)
+    W = O.random_weights(cfg, seed=17)
+    g = torch.Generator().manual_seed(18)
+    for i in range(2):
+        for name in ("q", "k", "v"):
+            W[f"l{i}.mix.{name}.conv"] = torch.randn(W[f"l{i}.mix.{name}"].shape[0], 1, generator=g)
+    toks = tokens(19, cfg["vocab"], 19)
+    want = O.forward(cfg, W, toks)
+    eng = make_engine(cfg, W)
+    close(feed(eng, 1, toks, [len(toks)]), want)
+    close(feed(eng, 2, toks, [2, 1, 5]), want)
+    plain = {k: v for k, v in W.items() if not k.endswith(".conv")}
+    assert (O.forward(cfg, plain, toks) - want).abs().max() > 1e-2
+
+
 def test_stream_after_every_layer(stack):
     W, toks, _ = stack
     handed = []

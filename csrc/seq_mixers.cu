@@ -1610,6 +1610,41 @@ row_gate_add_vec_kernel(T* __restrict__ acc, const T* __restrict__ y, const floa
   reinterpret_cast<Pack<T, PER>*>(acc)[i] = a;
 }
 
+// Router product in 32-bit: logits[t, r] = bias[r] + sum_c x[t, c] * w[r, c] with x in the activation type (its values
+// taken as they are: no 32-bit copy of the rows is made) and w, bias, logits fp32.  One warp per token, eight tokens per
+// CTA (the weights of the few router rows are re-read from L1 by the other warps); a lane takes 4 consecutive columns.
+constexpr int kRouterRows = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const T* __restrict__ x, long long ld, const float* __restrict__ w, const float* __restrict__ bias,
+                     float* __restrict__ out, int n_tokens, int width, int R) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tokens) return;
+  float acc[kRouterRows];
+#pragma unroll
+  for (int r = 0; r < kRouterRows; ++r) acc[r] = 0.f;
+  const T* row = x + (long long)t * ld;
+  for (int c = lane * 4; c < width; c += 128) {
+    float xv[4];
+    load_pack<T, 4>(row + c, xv, true, 4);
+#pragma unroll
+    for (int r = 0; r < kRouterRows; ++r) {
+      if (r < R) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + (long long)r * width + c);
+        acc[r] += (xv[0] * wv.x + xv[1] * wv.y) + (xv[2] * wv.z + xv[3] * wv.w);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kRouterRows; ++r) {
+    if (r < R) {
+      const float v = warp_sum(acc[r]);
+      if (lane == 0) out[(long long)t * R + r] = v + (bias ? bias[r] : 0.f);
+    }
+  }
+}
+
 template <typename T, int NV>
 static int launch_attention_tiles(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
                                   const void* atoms, int n_long, const void* tables, int max_blocks, int block_size,
@@ -1962,6 +1997,20 @@ SXB_API int sxb_row_gate_add(void* acc, const void* y, const void* gate, long lo
   }
   SEQMIX_DISPATCH(dtype, (row_gate_add_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
                              (T*)acc, (const T*)y, (const float*)gate, gate_ld, total, width)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* Router logits in 32-bit: out fp32 [n_tokens, R] = x[:, :width] w^T + bias; x `dtype` rows of pitch ld, w fp32 [R, width],
+ * bias fp32 [R] or null.  Up to 16 router rows, width and pitch multiples of 4, x and w 16-byte aligned. */
+SXB_API int sxb_router_logits(const void* x, long long ld, const void* w, const void* bias, void* out, int n_tokens,
+                              int width, int R, int dtype, void* stream) {
+  if (n_tokens <= 0 || R <= 0) return SXB_OK;
+  if (R > kRouterRows || width % 4 || ld % 4 ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) != 0)
+    return SXB_ERR_UNSUPPORTED;
+  SEQMIX_DISPATCH(dtype, (router_logits_kernel<T><<<(n_tokens + 7) / 8, 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)x, ld, (const float*)w, (const float*)bias, (float*)out, n_tokens, width, R)));
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }

@@ -529,6 +529,10 @@ int sxb_scale_softcap(void* x, long long total, float scale, float cap, void* st
 int sxb_row_gate_add(void* acc, const void* y, const void* gate, long long gate_ld, long long rows, int width,
                      int dtype, void* stream);
 
+/* ---- csrc/seq_mixers.cu */
+int sxb_router_logits(const void* x, long long ld, const void* w, const void* bias, void* out, int n_tokens,
+                      int width, int R, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

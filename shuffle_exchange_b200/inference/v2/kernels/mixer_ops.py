@@ -42,6 +42,7 @@ _lib.register({
     "sxb_side_gate": "p" "l" "p" "l" "pp" "iiii" "i" "p",
     "sxb_scale_softcap": "p" "l" "ff" "p",
     "sxb_row_gate_add": "ppp" "l" "l" "i" "i" "p",
+    "sxb_router_logits": "p" "l" "ppp" "iii" "i" "p",
 })
 
 _ACTS = {"identity": 0, "relu": 1, "gelu": 2, "silu": 3, "relu_sq": 4}
@@ -665,3 +666,23 @@ def row_gate_add_(acc: torch.Tensor, y: torch.Tensor, gate: torch.Tensor) -> tor
         return acc
     acc.copy_((acc.float() + torch.sigmoid(gate.float())[:, None] * y.float()).to(acc.dtype))
     return acc
+
+
+ROUTER_ROWS = 16         # router rows the fused product takes
+
+
+def router_logits(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 ``[T, R] = x w^T + bias`` with 32-bit products and sums: ``x`` ``[T, W]`` in the activation dtype (bf16 values
+    enter as they are), ``w`` fp32 ``[R, W]``, ``bias`` fp32 ``[R]``.  The kernel takes up to :data:`ROUTER_ROWS` rows and
+    widths that are multiples of 4; anything else is the library's fp32 product of the converted rows."""
+    T, W = x.shape
+    R = w.shape[0]
+    if (x.is_cuda and R <= ROUTER_ROWS and W % 4 == 0 and w.dtype == torch.float32 and w.is_contiguous()
+            and x.dtype in (torch.bfloat16, torch.float32) and x.stride(1) == 1
+            and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0
+            and (bias is None or bias.dtype == torch.float32)):
+        out = torch.empty(T, R, dtype=torch.float32, device=x.device)
+        _lib.call("sxb_router_logits", x.data_ptr(), x.stride(0), w.data_ptr(), _lib.ptr(bias), out.data_ptr(), T, W, R,
+                  _dt(x), _lib.stream_ptr())
+        return out
+    return torch.nn.functional.linear(x.float(), w.float(), None if bias is None else bias.float())

@@ -261,7 +261,9 @@ class DSMultiGemmMoE(DSMoEBase):
         """``gate_w`` ``[E (+ 1), H]``: the experts' router rows and, with ``shared_features``, one more row whose logit
         gates the shared expert ``shared = (w_up [Fs, H], w_down [H, Fs])``; ``gate_b`` the logits' bias."""
         c = self._config
-        if c.router_dtype is not None and _dt(c.router_dtype).torch != hidden_states.dtype:
+        if c.router_dtype is not None and _dt(c.router_dtype) == DtypeEnum.fp32 and gate_w.dtype == torch.float32:
+            logits = M.router_logits(hidden_states, gate_w, gate_b)       # 32-bit product straight from the 16-bit rows
+        elif c.router_dtype is not None and _dt(c.router_dtype).torch != hidden_states.dtype:
             rd = _dt(c.router_dtype).torch
             logits = torch.nn.functional.linear(hidden_states.to(rd), gate_w.to(rd), gate_b)
         else:

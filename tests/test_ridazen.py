@@ -246,6 +246,21 @@ def test_experts_router_bias_and_shared_expert(E, K, shared):
     assert bool((torch.topk(z, K).indices == E - 1).any(-1).all())
 
 
+@pytest.mark.parametrize("R,W,T,dt", [(9, 64, 37, torch.bfloat16), (3, 20, 5, torch.float32), (16, 256, 300, torch.bfloat16),
+                                      (17, 64, 4, torch.bfloat16), (4, 30, 9, torch.float32)])
+def test_router_product_in_32_bit(R, W, T, dt):
+    """16-bit rows enter the product as they are; weights, bias, products and sums are 32-bit (more rows than the kernel
+    takes, or a width that is not a multiple of 4, take the library product)."""
+    g = torch.Generator().manual_seed(R)
+    wide = torch.randn(T, W + 8, generator=g).to(dt)
+    xd = wide.to(DEV)[:, :W]                                         # a column slice: the row pitch exceeds the width
+    w, b = torch.randn(R, W, generator=g), torch.randn(R, generator=g)
+    want = wide[:, :W].double() @ w.double().T + b.double()
+    got = M.router_logits(xd, w.to(DEV), b.to(DEV))
+    assert got.dtype == torch.float32 and torch.allclose(got.double().cpu(), want, atol=1e-4, rtol=1e-5)
+    assert torch.allclose(M.router_logits(xd, w.to(DEV)).double().cpu(), want - b.double(), atol=1e-4, rtol=1e-5)
+
+
 def test_residual_step_with_multiplier_token_input_and_soft_cap():
     g = torch.Generator().manual_seed(11)
     T, W, dim, V = 7, 20, 6, 13

@@ -1611,28 +1611,35 @@ row_gate_add_vec_kernel(T* __restrict__ acc, const T* __restrict__ y, const floa
 }
 
 // Router product in 32-bit: logits[t, r] = bias[r] + sum_c x[t, c] * w[r, c] with x in the activation type (its values
-// taken as they are: no 32-bit copy of the rows is made) and w, bias, logits fp32.  One warp per token, eight tokens per
-// CTA (the weights of the few router rows are re-read from L1 by the other warps); a lane takes 4 consecutive columns.
+// taken as they are: no 32-bit copy of the rows is made) and w, bias, logits fp32.  CTAs of eight warps; WPT warps share
+// the columns of one token (prompt batches: one warp per token, eight tokens per CTA, the weights of the few router
+// rows are re-read from L1 by the other warps; few rows: the eight warps of a CTA split one token's columns and add
+// their parts in shared memory).  A lane takes 4 consecutive columns at a time.
 constexpr int kRouterRows = 16;
 
-template <typename T>
+template <typename T, int WPT>
 __global__ void __launch_bounds__(256)
 router_logits_kernel(const T* __restrict__ x, long long ld, const float* __restrict__ w, const float* __restrict__ bias,
                      float* __restrict__ out, int n_tokens, int width, int R) {
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (t >= n_tokens) return;
+  __shared__ float part_sum[8][kRouterRows];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int part = warp % WPT;
+  const int t = blockIdx.x * (8 / WPT) + warp / WPT;
+  const bool active = t < n_tokens;
   float acc[kRouterRows];
 #pragma unroll
   for (int r = 0; r < kRouterRows; ++r) acc[r] = 0.f;
-  const T* row = x + (long long)t * ld;
-  for (int c = lane * 4; c < width; c += 128) {
-    float xv[4];
-    load_pack<T, 4>(row + c, xv, true, 4);
+  if (active) {
+    const T* row = x + (long long)t * ld;
+    for (int c = (part * 32 + lane) * 4; c < width; c += 128 * WPT) {
+      float xv[4];
+      load_pack<T, 4>(row + c, xv, true, 4);
 #pragma unroll
-    for (int r = 0; r < kRouterRows; ++r) {
-      if (r < R) {
-        const float4 wv = *reinterpret_cast<const float4*>(w + (long long)r * width + c);
-        acc[r] += (xv[0] * wv.x + xv[1] * wv.y) + (xv[2] * wv.z + xv[3] * wv.w);
+      for (int r = 0; r < kRouterRows; ++r) {
+        if (r < R) {
+          const float4 wv = *reinterpret_cast<const float4*>(w + (long long)r * width + c);
+          acc[r] += (xv[0] * wv.x + xv[1] * wv.y) + (xv[2] * wv.z + xv[3] * wv.w);
+        }
       }
     }
   }
@@ -1640,7 +1647,19 @@ router_logits_kernel(const T* __restrict__ x, long long ld, const float* __restr
   for (int r = 0; r < kRouterRows; ++r) {
     if (r < R) {
       const float v = warp_sum(acc[r]);
-      if (lane == 0) out[(long long)t * R + r] = v + (bias ? bias[r] : 0.f);
+      if (WPT == 1) {
+        if (active && lane == 0) out[(long long)t * R + r] = v + (bias ? bias[r] : 0.f);
+      } else if (lane == 0) {
+        part_sum[warp][r] = v;
+      }
+    }
+  }
+  if (WPT > 1) {
+    __syncthreads();
+    if (active && part == 0 && lane < R) {
+      float v = bias ? bias[lane] : 0.f;
+      for (int p = 0; p < WPT; ++p) v += part_sum[warp + p][lane];
+      out[(long long)t * R + lane] = v;
     }
   }
 }
@@ -2009,8 +2028,13 @@ SXB_API int sxb_router_logits(const void* x, long long ld, const void* w, const 
   if (R > kRouterRows || width % 4 || ld % 4 ||
       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) != 0)
     return SXB_ERR_UNSUPPORTED;
-  SEQMIX_DISPATCH(dtype, (router_logits_kernel<T><<<(n_tokens + 7) / 8, 256, 0, (cudaStream_t)stream>>>(
-                             (const T*)x, ld, (const float*)w, (const float*)bias, (float*)out, n_tokens, width, R)));
+  if (n_tokens >= 1024) {
+    SEQMIX_DISPATCH(dtype, (router_logits_kernel<T, 1><<<(n_tokens + 7) / 8, 256, 0, (cudaStream_t)stream>>>(
+                               (const T*)x, ld, (const float*)w, (const float*)bias, (float*)out, n_tokens, width, R)));
+  } else {
+    SEQMIX_DISPATCH(dtype, (router_logits_kernel<T, 8><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
+                               (const T*)x, ld, (const float*)w, (const float*)bias, (float*)out, n_tokens, width, R)));
+  }
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }

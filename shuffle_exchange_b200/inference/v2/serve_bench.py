@@ -670,6 +670,11 @@ def ridazen_kernel_table(z: Dict, prefill: int, batch: int, context: int, timer,
             lambda: M.bias_act_rows(acc, wv, "identity"), T * W * 4)
         logits = torch.randn(T, E, device=dev)
         xe = torch.randn(T, W, device=dev).to(bf)
+        wr, br = torch.randn(E + 1, W, device=dev) / math.sqrt(W), torch.zeros(E + 1, device=dev)
+        add("router_logits (16-bit rows x fp32 weights, experts + shared gate)", None, phase,
+            lambda: M.router_logits(xe, wr, br), T * W * 2 + (E + 1) * W * 4 + T * (E + 1) * 4)
+        add("32-bit copy of the rows + library product", "router_logits (16-bit rows x fp32 weights, experts + shared gate)",
+            phase, lambda: torch.nn.functional.linear(xe.float(), wr, br), T * W * 2 + (E + 1) * W * 4 + T * (E + 1) * 4)
         w1 = (torch.randn(E, Fe, W, device=dev) / math.sqrt(W)).to(bf)
         w1g = (torch.randn(E, 2 * Fe, W, device=dev) / math.sqrt(W)).to(bf)
         w2 = (torch.randn(E, W, Fe, device=dev) / math.sqrt(Fe)).to(bf)

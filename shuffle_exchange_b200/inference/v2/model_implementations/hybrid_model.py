@@ -127,7 +127,10 @@ class DSHybridModel(DSInferenceModelBase):
     (+ ``norm2``, ``norm2b``, ``w_gate_up`` ``[2F, W]``, ``w_down`` with a feed-forward), ``w_in`` (the mixer's fused
     projection, rows in the order of the mixer module's ``projection layout``), ``wo``, and per kind: attention ``b_in``,
     ``sink`` (fp32); delta ``conv_w``, ``A_log``, ``dt_bias`` (fp32), ``norm``; ssd ``conv_w``, ``conv_b``, ``A_log``,
-    ``dt_bias``, ``D`` (fp32), ``norm``."""
+    ``dt_bias``, ``D`` (fp32), ``norm``.  Pre-scaled stacks: one norm weight per sublayer (``norm1``, ``norm2``), attention
+    with filtered projections ``conv_w``, ``q_norm``, ``k_norm``, ``dist_bias`` (fp32 ``[heads, distances]``); experts
+    ``moe_gate`` (fp32, the shared expert's gate row last), ``moe_gate_b``, ``moe_w1``, ``moe_w2``, ``shared_up``,
+    ``shared_down``; token input ``side_gate``, ``side_proj``, ``side_norm`` and the global ``side_embed``."""
 
     def __init__(self, spec: HybridSpec, weights: Dict, engine_config: RaggedInferenceEngineConfig, state_manager=None,
                  base_mp_group=None) -> None:

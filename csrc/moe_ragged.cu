@@ -92,6 +92,147 @@ top_k_gating_kernel(const T* __restrict__ logits, float* __restrict__ scores, in
   }
 }
 
+// Group-limited gating with a choice correction, one warp per token.  Scores are the softmax over all E router outputs
+// (fp32); the CHOICE is made by score + correction: the experts form n_groups equal groups of neighbours, a group's rank
+// is the largest choice value in it, only members of the keep_groups best groups can win, and the top_k largest choice
+// values among them are taken.  The weights are the winners' plain scores (no correction), divided by their sum + 1e-20
+// and multiplied by `scale`.  Outputs as top_k_gating_kernel.
+constexpr int kMaxGroups = 128;
+__global__ void __launch_bounds__(256)
+grouped_top_k_gating_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                            float* __restrict__ scores, int* __restrict__ assignments, int* __restrict__ offsets,
+                            int* __restrict__ expert_counts, int n_tokens, int n_experts, int top_k, int n_groups,
+                            int keep_groups, float scale) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= n_tokens) return;
+  const float* row = logits + (long long)warp * n_experts;
+  constexpr int PER = kMaxExperts / 32, PERG = kMaxGroups / 32;
+  float p[PER], ch[PER];               // plain score and choice value of the experts this lane holds
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = i * 32 + lane;
+    p[i] = (e < n_experts) ? row[e] : -INFINITY;
+    mx = fmaxf(mx, p[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    p[i] = (i * 32 + lane < n_experts) ? expf(p[i] - mx) : 0.f;
+    sum += p[i];
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  const int per_group = n_experts / n_groups;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = i * 32 + lane;
+    p[i] *= inv;
+    ch[i] = (e < n_experts) ? p[i] + (correction ? correction[e] : 0.f) : -INFINITY;
+  }
+  if (keep_groups < n_groups) {
+    // lane l keeps the rank of the groups l, l + 32, ...
+    float gmax[PERG];
+#pragma unroll
+    for (int j = 0; j < PERG; ++j) gmax[j] = -INFINITY;
+    for (int g = 0; g < n_groups; ++g) {
+      float m = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int e = i * 32 + lane;
+        if (e < n_experts && e / per_group == g) m = fmaxf(m, ch[i]);
+      }
+      m = warp_max(m);
+#pragma unroll
+      for (int j = 0; j < PERG; ++j)
+        if (j * 32 + lane == g) gmax[j] = m;
+    }
+    unsigned kept[PERG];               // bit l of kept[j]: group j * 32 + l stays (the same in every lane)
+#pragma unroll
+    for (int j = 0; j < PERG; ++j) kept[j] = 0u;
+    for (int k = 0; k < keep_groups; ++k) {
+      float best = -INFINITY;
+      int best_g = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < PERG; ++j) {
+        const int g = j * 32 + lane;
+        if (g < n_groups && (gmax[j] > best || (gmax[j] == best && g < best_g))) { best = gmax[j]; best_g = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (ob > best || (ob == best && og < best_g)) { best = ob; best_g = og; }
+      }
+      if (best_g >= n_groups) break;
+#pragma unroll
+      for (int j = 0; j < PERG; ++j) {
+        if (best_g / 32 == j) kept[j] |= 1u << (best_g & 31);
+        if (j * 32 + lane == best_g) gmax[j] = -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = i * 32 + lane;
+      if (e < n_experts) {
+        const int g = e / per_group;
+        bool in = false;
+#pragma unroll
+        for (int j = 0; j < PERG; ++j)
+          if (g / 32 == j) in = (kept[j] >> (g & 31)) & 1u;
+        if (!in) ch[i] = -INFINITY;
+      }
+    }
+  }
+  float picked_sum = 0.f;
+  float my_score[kMaxTopK];
+  int my_expert[kMaxTopK];
+  for (int k = 0; k < top_k; ++k) {
+    float best = -INFINITY, best_p = 0.f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = i * 32 + lane;
+      if (e < n_experts && (ch[i] > best || (ch[i] == best && e < best_e))) { best = ch[i]; best_e = e; best_p = p[i]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const float op = __shfl_xor_sync(0xffffffffu, best_p, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; best_p = op; }
+    }
+    if (best_e >= n_experts) { best_e = k; best_p = 0.f; }      // nothing comparable left: keep every index valid
+#pragma unroll
+    for (int i = 0; i < PER; ++i)
+      if (i * 32 + lane == best_e) ch[i] = -INFINITY;
+    my_score[k] = best_p;
+    my_expert[k] = best_e;
+    picked_sum += best_p;
+  }
+  if (lane == 0) {
+    const float norm = scale / (picked_sum + 1e-20f);
+    for (int k = 0; k < top_k; ++k) {
+      const long long o = (long long)warp * top_k + k;
+      scores[o] = my_score[k] * norm;
+      assignments[o] = my_expert[k];
+      offsets[o] = atomicAdd(&expert_counts[my_expert[k]], 1);
+    }
+  }
+}
+
+// dst rows [offsets[g_lo], offsets[g_hi]) = the same rows of src (row_vec 16-byte words each): experts that hand their
+// input on unchanged, between the grouped products of the others.  offsets int32 on the device; one CTA per row.
+__global__ void __launch_bounds__(128)
+copy_group_rows_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, const int* __restrict__ offsets, int g_lo,
+                       int g_hi, int row_vec) {
+  const long long lo = offsets[g_lo], hi = offsets[g_hi];
+  for (long long r = lo + blockIdx.x; r < hi; r += gridDim.x)
+    for (int i = threadIdx.x; i < row_vec; i += blockDim.x) dst[r * row_vec + i] = src[r * row_vec + i];
+}
+
 // Exclusive scan of expert_counts -> expert_cumsum[E] (INCLUSIVE cumulative ends, the layout the grouped GEMM wants:
 // rows of expert e are [cumsum[e-1], cumsum[e])).  Single CTA, E <= 1024.
 __global__ void __launch_bounds__(1024)
@@ -427,6 +568,43 @@ SXB_API int sxb_top_k_gating(const void* logits, void* scores, void* assignments
     case kF32: moe::top_k_gating_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(logits), sc, as, of, ec, n_tokens, n_experts, top_k, renormalize); break;
     default: return SXB_ERR_UNSUPPORTED;
   }
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+// Group-limited gating with a choice correction.  logits fp32 [T, E]; correction fp32 [E] or null; the E experts form
+// n_groups equal groups of neighbours of which the keep_groups whose best (score + correction) is largest stay eligible;
+// the top_k largest (score + correction) among them win; scores fp32 [T, K] = softmax score of the winner / (sum of the
+// winners' scores + 1e-20) * scale; assignments / offsets / expert_counts as sxb_top_k_gating.
+SXB_API int sxb_grouped_top_k_gating(const void* logits, const void* correction, void* scores, void* assignments,
+                                     void* offsets, void* expert_counts, int n_tokens, int n_experts, int top_k,
+                                     int n_groups, int keep_groups, float scale, void* stream) {
+  if (n_tokens <= 0) return SXB_OK;
+  if (n_experts <= 0 || n_experts > moe::kMaxExperts || top_k <= 0 || top_k > moe::kMaxTopK || top_k > n_experts)
+    return SXB_ERR_BAD_ARG;
+  if (n_groups <= 0 || n_groups > moe::kMaxGroups || n_experts % n_groups || keep_groups <= 0 || keep_groups > n_groups ||
+      top_k > keep_groups * (n_experts / n_groups))
+    return SXB_ERR_BAD_ARG;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaMemsetAsync(expert_counts, 0, sizeof(int) * n_experts, s);
+  moe::grouped_top_k_gating_kernel<<<(unsigned)((n_tokens + 7) / 8), 256, 0, s>>>(
+      static_cast<const float*>(logits), static_cast<const float*>(correction), static_cast<float*>(scores),
+      static_cast<int*>(assignments), static_cast<int*>(offsets), static_cast<int*>(expert_counts), n_tokens, n_experts,
+      top_k, n_groups, keep_groups, scale);
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+// dst rows [offsets[g_lo], offsets[g_hi]) <- src rows of the same range; rows of row_bytes (a multiple of 16) bytes,
+// offsets int32 on the device (group row offsets of an expert-sorted buffer), max_rows bounds the grid.
+SXB_API int sxb_copy_group_rows(const void* src, void* dst, const void* offsets, int g_lo, int g_hi, int row_bytes,
+                                long long max_rows, void* stream) {
+  if (max_rows <= 0 || g_hi <= g_lo) return SXB_OK;
+  if (row_bytes % 16 || ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return SXB_ERR_UNSUPPORTED;
+  const unsigned blocks = (unsigned)(max_rows < 2048 ? max_rows : 2048);
+  moe::copy_group_rows_kernel<<<blocks, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), static_cast<const int*>(offsets), g_lo, g_hi,
+      row_bytes / 16);
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }

@@ -65,14 +65,15 @@ embed_sinusoid_kernel(const int* __restrict__ ids, const int* __restrict__ pos, 
 }
 
 // ------------------------------------------------------------------------------------------------ residual + norms
-// One CTA per row.  y (optional): residual += mult * y / rms(y) * w_post, or += mult * y without w_post.  extra
-// (optional): residual += extra.  w_pre (optional): out = residual / rms(residual) * w_pre; out without w_pre: the
-// residual itself in the activation type.
+// One CTA per row.  y (optional): residual += mult * y / rms(y) * w_post, or += mult * y without w_post; with y_scale
+// the addend is also multiplied per channel by y_scale.  extra (optional): residual += extra.  w_pre (optional):
+// out = residual / rms(residual) * (w_add + w_pre) (w_add 1 for weights stored as their distance from one); out without
+// w_pre: the residual itself in the activation type.
 template <typename T>
 __global__ void __launch_bounds__(256)
 resid_norm_step_kernel(float* __restrict__ resid, const T* __restrict__ y, const T* __restrict__ w_post,
                        const float* __restrict__ extra, const T* __restrict__ w_pre, T* __restrict__ out, int width,
-                       float eps, float mult) {
+                       float eps, float mult, const T* __restrict__ y_scale, float w_add) {
   __shared__ float red[32];
   const long long base = (long long)blockIdx.x * width;
   float* r = resid + base;
@@ -89,7 +90,11 @@ resid_norm_step_kernel(float* __restrict__ resid, const T* __restrict__ y, const
   float ss2 = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float v = r[c];
-    if (y != nullptr) v += to_f32<T>(y[base + c]) * inv_y * (w_post ? to_f32<T>(w_post[c]) : 1.f);
+    if (y != nullptr) {
+      float add = to_f32<T>(y[base + c]) * inv_y * (w_post ? to_f32<T>(w_post[c]) : 1.f);
+      if (y_scale != nullptr) add *= to_f32<T>(y_scale[c]);
+      v += add;
+    }
     if (extra != nullptr) v += extra[base + c];
     if (y != nullptr || extra != nullptr) r[c] = v;
     ss2 += v * v;
@@ -102,7 +107,7 @@ resid_norm_step_kernel(float* __restrict__ resid, const T* __restrict__ y, const
   ss2 = block_sum(ss2, red);
   const float inv = 1.f / sqrtf(ss2 / (float)width + eps);
   for (int c = threadIdx.x; c < width; c += blockDim.x)
-    out[base + c] = from_f32<T>(r[c] * inv * to_f32<T>(w_pre[c]));
+    out[base + c] = from_f32<T>(r[c] * inv * (w_add + to_f32<T>(w_pre[c])));
 }
 
 // ------------------------------------------------------------------------------------------------ attention
@@ -884,6 +889,23 @@ recurrence_gates_kernel(const T* __restrict__ a_raw, const T* __restrict__ b_raw
   beta[i] = mode == 0 ? sigmoid_f(to_f32<T>(b_raw[(long long)t * ld + h])) : dt;
 }
 
+// Decay per head AND key channel:  decay[t, h, c] = exp(-exp(A_log[h]) * softplus(a_raw[t, h n + c] + dt_bias[h n + c])),
+// beta[t, h] = sigmoid(b_raw[t, h]).  a_raw rows of pitch lda hold H n channels, b_raw rows of pitch ldb hold H.
+template <typename T>
+__global__ void __launch_bounds__(256)
+channel_decay_gates_kernel(const T* __restrict__ a_raw, long long lda, const T* __restrict__ b_raw, long long ldb,
+                           const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                           float* __restrict__ decay, float* __restrict__ beta, int H, int n, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int Hn = H * n;
+  const long long t = i / Hn;
+  const int c = (int)(i % Hn), h = c / n;
+  const float dt = softplus_f(to_f32<T>(a_raw[t * lda + c]) + dt_bias[c]);
+  decay[i] = expf(-expf(A_log[h]) * dt);
+  if (c < H) beta[t * H + c] = sigmoid_f(to_f32<T>(b_raw[t * ldb + c]));
+}
+
 // ------------------------------------------------------------------------------------------------ recurrence
 // State per (slot, head): dv columns of n floats, stored [dv][n].  Each output column evolves on its own:
 //   s <- a s;  u = b (v_c - [delta] s.k);  s <- s + k u;  o_c = s.q (+ D v_c)
@@ -893,7 +915,7 @@ recurrence_gates_kernel(const T* __restrict__ a_raw, const T* __restrict__ b_raw
 // is the same and the longer shuffle trees add instructions.)  The products run as packed pairs (fma.f32x2).
 constexpr int kRecThreads = 128, kTB = 8;
 
-template <int R, bool DELTA, int LPC>
+template <int R, bool DELTA, int LPC, bool CHAN>
 __global__ void __launch_bounds__(kRecThreads)
 linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict__ qvec, long long ldkq,
                          const float* __restrict__ val, long long ldv, const float* __restrict__ decay,
@@ -902,10 +924,11 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
   // Lane l of a column holds the float4 chunks l, l + LPC, l + 2 LPC, ... of the column's n-vector (padded with zeros
   // to NP = LPC R), so k, q and the state move as 16-byte words without bank conflicts.  Two staging buffers, each
   // k [TB][NP] | q [TB][NP] | v [TB][COLS] | decay [TB] | beta [TB]: the next TB tokens are copied in (cp.async) while
-  // the current ones are walked.
+  // the current ones are walked.  CHAN: the decay is a vector over the key channels (decay [rows, H n]) and follows the
+  // scalars as one more [TB][NP] block; the state is multiplied by it chunk by chunk before the delta rule's product.
   constexpr int NP = R * LPC, R4 = R / 4, COLS = kRecThreads / LPC;
   extern __shared__ __align__(16) float sm[];
-  constexpr int stage = 2 * kTB * NP + kTB * COLS + 2 * kTB;
+  constexpr int stage = (CHAN ? 3 : 2) * kTB * NP + kTB * COLS + 2 * kTB;
   const int* si = seq_info + 4 * blockIdx.z;
   const int first = si[0], rows = si[1], seen = si[2], slot = si[3];
   const int h = blockIdx.y, g = h / (H / G);
@@ -943,7 +966,23 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
     float* sv = sq + kTB * NP;
     float* sa = sv + kTB * COLS;
     float* sb = sa + kTB;
+    float* sg = sb + kTB;
     const int nt = min(kTB, rows - t0);
+    if (CHAN) {
+      const long long Hn = (long long)H * n;
+      if (n4) {
+        const int nq4 = n >> 2;
+        for (int i = threadIdx.x; i < nt * nq4; i += blockDim.x) {
+          const int tt = i / nq4, c = (i % nq4) * 4;
+          __pipeline_memcpy_async(sg + tt * NP + c, decay + (long long)(first + t0 + tt) * Hn + (long long)h * n + c, 16);
+        }
+      } else {
+        for (int i = threadIdx.x; i < nt * n; i += blockDim.x) {
+          const int tt = i / n, c = i % n;
+          __pipeline_memcpy_async(sg + tt * NP + c, decay + (long long)(first + t0 + tt) * Hn + (long long)h * n + c, 4);
+        }
+      }
+    }
     if (wide_copy) {
       const int nq4 = n >> 2;
       for (int i = threadIdx.x; i < nt * nq4; i += blockDim.x) {
@@ -965,7 +1004,7 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
       __pipeline_memcpy_async(sv + i, val + (long long)(first + t0 + i / COLS) * ldv + h * dv + c, 4);
     }
     for (int i = threadIdx.x; i < nt; i += blockDim.x) {
-      __pipeline_memcpy_async(sa + i, decay + (long long)(first + t0 + i) * H + h, 4);
+      if (!CHAN) __pipeline_memcpy_async(sa + i, decay + (long long)(first + t0 + i) * H + h, 4);
       __pipeline_memcpy_async(sb + i, beta + (long long)(first + t0 + i) * H + h, 4);
     }
     __pipeline_commit();
@@ -985,26 +1024,39 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
     const float* sv = sq + kTB * NP;
     const float* sa = sv + kTB * COLS;
     const float* sb = sa + kTB;
+    const float* sg = sb + kTB;
     // One token.  A full group of TB tokens is walked by straight-line code, so the loads of k and q and the read-out
     // reductions of neighbouring tokens overlap the serial part (the state update, and the dot product before it for
     // the delta rule).
     struct Tok {                      // one token's operands, loaded one token ahead of their use
       float a, b, v;
-      float4 k[R4], q[R4];
+      float4 k[R4], q[R4], g[CHAN ? R4 : 1];
     };
     auto fetch = [&](int tt) {
       Tok t;
-      t.a = sa[tt], t.b = sb[tt], t.v = sv[tt * COLS + lc];
+      t.a = CHAN ? 1.f : sa[tt], t.b = sb[tt], t.v = sv[tt * COLS + lc];
       const float4* kk = reinterpret_cast<const float4*>(sk + tt * NP) + l;
       const float4* qq = reinterpret_cast<const float4*>(sq + tt * NP) + l;
 #pragma unroll
       for (int r4 = 0; r4 < R4; ++r4) t.k[r4] = kk[r4 * LPC], t.q[r4] = qq[r4 * LPC];
+      if (CHAN) {
+        const float4* gg = reinterpret_cast<const float4*>(sg + tt * NP) + l;
+#pragma unroll
+        for (int r4 = 0; r4 < R4; ++r4) t.g[r4] = gg[r4 * LPC];
+      }
       return t;
     };
     auto step = [&](const Tok& t, float& o_lane) {
       const float a = t.a, b = t.b, v = t.v;
       const float4* k4 = t.k;
       float u = b * v;
+      if (CHAN) {                      // the decayed state enters the product below: decay first, a stays 1
+#pragma unroll
+        for (int r4 = 0; r4 < R4; ++r4) {
+          S[2 * r4] = __fmul2_rn(S[2 * r4], make_float2(t.g[r4].x, t.g[r4].y));
+          S[2 * r4 + 1] = __fmul2_rn(S[2 * r4 + 1], make_float2(t.g[r4].z, t.g[r4].w));
+        }
+      }
       if (DELTA) {                     // (a S)^T k = a (S^T k): the decay is folded into the update below
         float2 d01 = make_float2(0.f, 0.f), d23 = make_float2(0.f, 0.f);
 #pragma unroll
@@ -1022,8 +1074,9 @@ linear_recurrence_kernel(const float* __restrict__ kvec, const float* __restrict
 #pragma unroll
       for (int r4 = 0; r4 < R4; ++r4) {
         const float4 q4 = t.q[r4];
-        S[2 * r4] = __ffma2_rn(make_float2(k4[r4].x, k4[r4].y), u2, __fmul2_rn(S[2 * r4], a2));
-        S[2 * r4 + 1] = __ffma2_rn(make_float2(k4[r4].z, k4[r4].w), u2, __fmul2_rn(S[2 * r4 + 1], a2));
+        S[2 * r4] = __ffma2_rn(make_float2(k4[r4].x, k4[r4].y), u2, CHAN ? S[2 * r4] : __fmul2_rn(S[2 * r4], a2));
+        S[2 * r4 + 1] = __ffma2_rn(make_float2(k4[r4].z, k4[r4].w), u2,
+                                   CHAN ? S[2 * r4 + 1] : __fmul2_rn(S[2 * r4 + 1], a2));
         o01 = __ffma2_rn(S[2 * r4], make_float2(q4.x, q4.y), o01);
         o23 = __ffma2_rn(S[2 * r4 + 1], make_float2(q4.z, q4.w), o23);
       }
@@ -1088,16 +1141,18 @@ group_norm_gate_kernel(const float* __restrict__ y, const T* __restrict__ gate, 
   const int t = blockIdx.x, c0 = blockIdx.y * gs;
   const float* yr = y + (long long)t * C + c0;
   const T* gr = gate + (long long)t * ldg + c0;
+  const bool sigm = (gate_first & 2) != 0;      // bit 1: the gate is sigmoid(gate) instead of silu(gate)
+  gate_first &= 1;
   float ss = 0.f;
   for (int c = threadIdx.x; c < gs; c += blockDim.x) {
     float v = yr[c];
-    if (gate_first) v *= silu_f(to_f32<T>(gr[c]));
+    if (gate_first) v *= sigm ? sigmoid_f(to_f32<T>(gr[c])) : silu_f(to_f32<T>(gr[c]));
     ss += v * v;
   }
   ss = block_sum(ss, red);
   const float inv = 1.f / sqrtf(ss / (float)gs + eps);
   for (int c = threadIdx.x; c < gs; c += blockDim.x) {
-    const float sg = silu_f(to_f32<T>(gr[c]));
+    const float sg = sigm ? sigmoid_f(to_f32<T>(gr[c])) : silu_f(to_f32<T>(gr[c]));
     const float wv = to_f32<T>(w[(c0 + c) % wlen]);
     const float v = gate_first ? yr[c] * sg * inv * wv : yr[c] * inv * wv * sg;
     out[(long long)t * C + c0 + c] = from_f32<T>(v);
@@ -1106,14 +1161,18 @@ group_norm_gate_kernel(const float* __restrict__ y, const T* __restrict__ gate, 
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-gated_act_rows_kernel(const T* __restrict__ in, T* __restrict__ out, long long total, int F, int act) {
+gated_act_rows_kernel(const T* __restrict__ in, T* __restrict__ out, long long total, int F, int act, float limit) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long r = i / F;
   const int c = (int)(i % F);
-  const float gte = to_f32<T>(in[r * 2 * F + c]), up = to_f32<T>(in[r * 2 * F + F + c]);
+  float gte = to_f32<T>(in[r * 2 * F + c]), up = to_f32<T>(in[r * 2 * F + F + c]);
   float a;
-  if (act == 2) {
+  if (act == 5) {          // clamped: g = min(gate, limit), u = clamp(up, -limit, limit); g sigmoid(1.702 g) (u + 1)
+    gte = fminf(gte, limit);
+    up = fminf(fmaxf(up, -limit), limit) + 1.f;
+    a = gte * sigmoid_f(1.702f * gte);
+  } else if (act == 2) {
     a = 0.5f * gte * (1.f + tanhf(0.7978845608028654f * (gte + 0.044715f * gte * gte * gte)));
   } else if (act == 3) {
     a = silu_f(gte);
@@ -1266,16 +1325,18 @@ bias_act_rows_vec_kernel(const T* __restrict__ in, const T* __restrict__ bias, T
 // channels) followed by one rotated key part (rot channels) that all heads share; a query head meets them as
 // [q_abs | q_rot], q_abs its unrotated part carried through the key up-projection.  One CTA per token:
 //   cache[slot] = [ latent / rms * w_norm | rope(k_rot) ],  q_out[t, h] = [ q_abs[t, h] | rope(q[t, h, dim:]) ]  (fp32)
-// rope turns the pairs (2i, 2i+1), i < rot_dims / 2, by pos * inv_freq[i]; channels from rot_dims on pass unchanged.
+// rope turns the pairs (2i, 2i+1), i < rot_dims / 2, by pos * inv_freq[i] and multiplies them by amp (cos and sin both
+// carry the factor); channels from rot_dims on pass unchanged.
 template <typename T>
 __device__ __forceinline__ void rope_pairs(const T* __restrict__ src, int rot, int rot_dims, float pos,
                                            const float* __restrict__ inv_freq, int lane, int stride, float* dst32,
-                                           T* dstT) {
+                                           T* dstT, float amp) {
   for (int i = lane; i < rot; i += stride) {
     float v = to_f32<T>(src[i]);
     if (i < rot_dims) {
       float sn, cs;
       sincosf(pos * inv_freq[i >> 1], &sn, &cs);
+      sn *= amp, cs *= amp;
       const float other = to_f32<T>(src[i ^ 1]);
       v = (i & 1) ? v * cs + other * sn : v * cs - other * sn;
     }
@@ -1291,7 +1352,7 @@ latent_qk_prepare_kernel(const T* __restrict__ qfull, long long ldq, const T* __
                          const float* __restrict__ inv_freq, float* __restrict__ q_out, T* __restrict__ cache,
                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                          const int* __restrict__ tables, int max_blocks, int block_size, int H, int dim, int rot, int r,
-                         int rot_dims, float eps) {
+                         int rot_dims, float eps, float amp) {
   __shared__ float red[32];
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int p = tok_pos[t];
@@ -1308,14 +1369,14 @@ latent_qk_prepare_kernel(const T* __restrict__ qfull, long long ldq, const T* __
   const float inv = 1.f / sqrtf(ss / (float)r + eps);
   for (int c = threadIdx.x; c < r; c += blockDim.x)
     crow[c] = from_f32<T>(to_f32<T>(kr[c]) * inv * to_f32<T>(w_norm[c]));
-  rope_pairs<T>(kr + r, rot, rot_dims, pos, inv_freq, threadIdx.x, blockDim.x, nullptr, crow + r);
+  rope_pairs<T>(kr + r, rot, rot_dims, pos, inv_freq, threadIdx.x, blockDim.x, nullptr, crow + r, amp);
   const int d = r + rot;
   for (int h = warp; h < H; h += nw) {
     float* qo = q_out + ((long long)t * H + h) * d;
     const T* qa = qabs + (long long)t * qa_tok + (long long)h * qa_head;
     for (int c = lane; c < r; c += 32) qo[c] = to_f32<T>(qa[c]);
     rope_pairs<T>(qfull + (long long)t * ldq + (long long)h * (dim + rot) + dim, rot, rot_dims, pos, inv_freq, lane, 32,
-                  qo + r, nullptr);
+                  qo + r, nullptr, amp);
   }
 }
 
@@ -1450,17 +1511,18 @@ SXB_API int sxb_embed_sinusoid(const void* ids, const void* pos, const void* tab
   return SXB_OK;
 }
 
-/* Per row of the fp32 residual [rows, width]: if y: residual += mult * y / rms(y) * w_post (without w_post: += mult * y);
- * if extra (fp32): residual += extra; if w_pre: out = residual / rms(residual) * w_pre (out without w_pre: the residual in
- * `dtype`).  y, w_post, w_pre, out are `dtype`; any of the parts may be absent (null). */
+/* Per row of the fp32 residual [rows, width]: if y: residual += mult * y / rms(y) * w_post (without w_post: += mult * y),
+ * the addend times y_scale per channel if given; if extra (fp32): residual += extra; if w_pre: out = residual /
+ * rms(residual) * (w_add + w_pre) (out without w_pre: the residual in `dtype`).  y, w_post, w_pre, y_scale, out are
+ * `dtype`; any of the parts may be absent (null). */
 SXB_API int sxb_resid_norm_step(void* resid, const void* y, const void* w_post, const void* extra, const void* w_pre,
                                 void* out, long long rows, int width, float eps, float mult, int dtype,
-                                void* stream) {
+                                const void* y_scale, float w_add, void* stream) {
   if (rows <= 0) return SXB_OK;
   if ((y == nullptr && w_post != nullptr) || (w_pre != nullptr && out == nullptr)) return SXB_ERR_BAD_ARG;
   SEQMIX_DISPATCH(dtype, (resid_norm_step_kernel<T><<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
                              (float*)resid, (const T*)y, (const T*)w_post, (const float*)extra, (const T*)w_pre,
-                             (T*)out, width, eps, mult)));
+                             (T*)out, width, eps, mult, (const T*)y_scale, w_add)));
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }
@@ -1792,31 +1854,40 @@ SXB_API int sxb_recurrence_gates(const void* a_raw, const void* b_raw, long long
   return SXB_OK;
 }
 
-/* Per sequence and head, rows in order:  S <- decay S;  u = beta (v - [delta] S^T k);  S <- S + k u^T;
+/* decay_channels != 0: decay fp32 [rows, H * n] holds one factor per head and key channel (the rows of S that belong to
+ * that channel are multiplied by it).
+ * Per sequence and head, rows in order:  S <- decay S;  u = beta (v - [delta] S^T k);  S <- S + k u^T;
  * o = S^T q (+ skip[h] v).  kvec / qvec fp32 [rows, ldkq] hold G heads of n channels, val fp32 [rows, ldv] H heads of dv,
  * decay / beta fp32 [rows, H], state fp32 [slots, H, dv, n] (taken as zero when the sequence has seen no token), out fp32
  * [rows, H * dv]. */
 SXB_API int sxb_linear_recurrence(const void* kvec, const void* qvec, long long ldkq, const void* val, long long ldv,
                                   const void* decay, const void* beta, const void* skip, void* state, void* out,
                                   const void* seq_info, int n_seqs, int H, int G, int n, int dv, int delta,
-                                  void* stream) {
+                                  int decay_channels, void* stream) {
   if (n_seqs <= 0) return SXB_OK;
   if (n > 256 || H % G) return SXB_ERR_UNSUPPORTED;
   cudaStream_t s = (cudaStream_t)stream;
-#define LAUNCH_REC(R, D, LPC)                                                                                       \
+#define LAUNCH_REC(R, D, LPC, CH)                                                                                   \
   do {                                                                                                              \
     constexpr int cols = kRecThreads / LPC;                                                                         \
-    const size_t smem = (size_t)2 * (2 * kTB * (R * LPC) + kTB * cols + 2 * kTB) * sizeof(float);                   \
-    linear_recurrence_kernel<R, D, LPC><<<dim3((dv + cols - 1) / cols, H, n_seqs), kRecThreads, smem, s>>>(         \
+    const size_t smem = (size_t)2 * ((CH ? 3 : 2) * kTB * (R * LPC) + kTB * cols + 2 * kTB) * sizeof(float);        \
+    if (smem > 48 * 1024)                                                                                           \
+      cudaFuncSetAttribute(linear_recurrence_kernel<R, D, LPC, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                           (int)smem);                                                                              \
+    linear_recurrence_kernel<R, D, LPC, CH><<<dim3((dv + cols - 1) / cols, H, n_seqs), kRecThreads, smem, s>>>(     \
         (const float*)kvec, (const float*)qvec, ldkq, (const float*)val, ldv, (const float*)decay,                  \
         (const float*)beta, (const float*)skip, (float*)state, (float*)out, (const int*)seq_info, H, G, n, dv);     \
   } while (0)
-#define LAUNCH_REC_N(D)                                  \
-  if (n <= 32) LAUNCH_REC(4, D, 8);                      \
-  else if (n <= 64) LAUNCH_REC(8, D, 8);                 \
-  else if (n <= 128) LAUNCH_REC(16, D, 8);               \
-  else LAUNCH_REC(32, D, 8)
-  if (delta) { LAUNCH_REC_N(true); } else { LAUNCH_REC_N(false); }
+#define LAUNCH_REC_N(D, CH)                                  \
+  if (n <= 32) LAUNCH_REC(4, D, 8, CH);                      \
+  else if (n <= 64) LAUNCH_REC(8, D, 8, CH);                 \
+  else if (n <= 128) LAUNCH_REC(16, D, 8, CH);               \
+  else LAUNCH_REC(32, D, 8, CH)
+  if (decay_channels) {
+    if (delta) { LAUNCH_REC_N(true, true); } else { LAUNCH_REC_N(false, true); }
+  } else {
+    if (delta) { LAUNCH_REC_N(true, false); } else { LAUNCH_REC_N(false, false); }
+  }
 #undef LAUNCH_REC_N
 #undef LAUNCH_REC
   SXB_CHECK_LAUNCH();
@@ -1824,7 +1895,8 @@ SXB_API int sxb_linear_recurrence(const void* kvec, const void* qvec, long long 
 }
 
 /* RMS norm over groups of gs channels of y fp32 [n_tokens, C] with a SiLU gate (`dtype` rows of pitch ldg) and a weight
- * of wlen entries that repeats along the row.  gate_first: norm(y silu(gate)) w; else norm(y) w silu(gate). */
+ * of wlen entries that repeats along the row.  gate_first bit 0: norm(y silu(gate)) w; else norm(y) w silu(gate); bit 1:
+ * sigmoid(gate) in place of silu(gate). */
 SXB_API int sxb_group_norm_gate(const void* y, const void* gate, long long ldg, const void* w, int wlen, void* out,
                                 int n_tokens, int C, int gs, float eps, int gate_first, int dtype, void* stream) {
   if (n_tokens <= 0) return SXB_OK;
@@ -1836,12 +1908,14 @@ SXB_API int sxb_group_norm_gate(const void* y, const void* gate, long long ldg, 
   return SXB_OK;
 }
 
-/* out [rows, F] = act(in[:, :F]) * in[:, F:] for rows of any width; act: 0 identity, 1 relu, 2 gelu (tanh form), 3 silu. */
-SXB_API int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act, int dtype, void* stream) {
+/* out [rows, F] = act(in[:, :F]) * in[:, F:] for rows of any width; act: 0 identity, 1 relu, 2 gelu (tanh form), 3 silu,
+ * 5 clamped: g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(1.702 g) (u + 1). */
+SXB_API int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act, int dtype, float limit,
+                               void* stream) {
   const long long total = rows * F;
   if (total <= 0) return SXB_OK;
   SEQMIX_DISPATCH(dtype, (gated_act_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-                             (const T*)in, (T*)out, total, F, act)));
+                             (const T*)in, (T*)out, total, F, act, limit)));
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }
@@ -1919,19 +1993,20 @@ SXB_API int sxb_bias_act_rows(const void* in, const void* bias, void* out, long 
 /* Latent attention, per token: cache[page, offset] = [kv[:r] / rms * w_norm | rope(kv[r : r+rot])] (`dtype`
  * [pages, block_size, r + rot]); q_out fp32 [n_tokens, H, r + rot] = [qabs[t, h] | rope(qfull[t, h, dim : dim+rot])].
  * qfull rows of pitch ldq hold H heads of dim + rot; qabs element (t, h, c) at t * qa_tok + h * qa_head + c; kv rows of
- * pitch ldkv; inv_freq fp32 [rot_dims / 2]. */
+ * pitch ldkv; inv_freq fp32 [rot_dims / 2]; amp multiplies the turned channels of q and k. */
 SXB_API int sxb_latent_qk_prepare(const void* qfull, long long ldq, const void* qabs, long long qa_tok,
                                   long long qa_head, const void* kv, long long ldkv, const void* w_norm,
                                   const void* inv_freq, void* q_out, void* cache, const void* tok_seq,
                                   const void* tok_pos, const void* tables, int n_tokens, int max_blocks, int block_size,
-                                  int H, int dim, int rot, int r, int rot_dims, float eps, int dtype, void* stream) {
+                                  int H, int dim, int rot, int r, int rot_dims, float eps, int dtype, float amp,
+                                  void* stream) {
   if (n_tokens <= 0) return SXB_OK;
   if (rot_dims > rot || (rot_dims & 1)) return SXB_ERR_BAD_ARG;
   SEQMIX_DISPATCH(dtype, (latent_qk_prepare_kernel<T><<<n_tokens, 128, 0, (cudaStream_t)stream>>>(
                              (const T*)qfull, ldq, (const T*)qabs, qa_tok, qa_head, (const T*)kv, ldkv,
                              (const T*)w_norm, (const float*)inv_freq, (float*)q_out, (T*)cache, (const int*)tok_seq,
                              (const int*)tok_pos, (const int*)tables, max_blocks, block_size, H, dim, rot, r, rot_dims,
-                             eps)));
+                             eps, amp)));
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }
@@ -2035,6 +2110,133 @@ SXB_API int sxb_router_logits(const void* x, long long ld, const void* w, const 
     SEQMIX_DISPATCH(dtype, (router_logits_kernel<T, 8><<<n_tokens, 256, 0, (cudaStream_t)stream>>>(
                                (const T*)x, ld, (const float*)w, (const float*)bias, (float*)out, n_tokens, width, R)));
   }
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ gates and activations
+namespace sxb {
+namespace seqmix {
+
+// x[t, c] *= sigmoid(gate[t, c / group]) in place: group 1 is one gate per channel, group = head size one per head.
+template <typename T>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_rows_kernel(T* __restrict__ x, const T* __restrict__ gate, long long ldg, long long total, int width,
+                         int group) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / width;
+  const int c = (int)(i % width);
+  x[i] = from_f32<T>(to_f32<T>(x[i]) * sigmoid_f(to_f32<T>(gate[t * ldg + c / group])));
+}
+
+// The same with 8 (bf16) or 4 (fp32) consecutive channels per thread: 16-byte accesses of x, and of the gate when it is
+// per channel; a per-head gate is read once per thread (group is then a multiple of the vector length).
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_rows_vec_kernel(T* __restrict__ x, const T* __restrict__ gate, long long ldg, long long nvec, int wvec,
+                             int group) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const long long t = i / wvec;
+  const int c = (int)(i % wvec) * VEC;
+  struct alignas(16) Pack { T v[VEC]; };
+  Pack xv = *reinterpret_cast<const Pack*>(x + i * VEC);
+  if (group == 1) {
+    const Pack gv = *reinterpret_cast<const Pack*>(gate + t * ldg + c);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) xv.v[j] = from_f32<T>(to_f32<T>(xv.v[j]) * sigmoid_f(to_f32<T>(gv.v[j])));
+  } else {
+    const float s = sigmoid_f(to_f32<T>(gate[t * ldg + c / group]));
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) xv.v[j] = from_f32<T>(to_f32<T>(xv.v[j]) * s);
+  }
+  *reinterpret_cast<Pack*>(x + i * VEC) = xv;
+}
+
+// Three-power normalised activation, one CTA per row of F channels:
+//   z = x + bias;  out = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e,   rms(u) = sqrt(mean(u^2) + eps)
+// coef fp32 [4] = (a, b, c, e).  The three sums of squares (z^2, z^4, z^6) come from one pass in 32-bit.
+template <typename T>
+__global__ void __launch_bounds__(256)
+power_norm_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, const float* __restrict__ coef,
+                      T* __restrict__ out, int F, float eps) {
+  __shared__ float red[32];
+  const long long base = (long long)blockIdx.x * F;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int c = threadIdx.x; c < F; c += blockDim.x) {
+    const float z = to_f32<T>(x[base + c]) + (bias ? to_f32<T>(bias[c]) : 0.f);
+    const float z2 = z * z;
+    s1 += z2, s2 += z2 * z2, s3 += z2 * z2 * z2;
+  }
+  s1 = block_sum(s1, red);
+  __syncthreads();
+  s2 = block_sum(s2, red);
+  __syncthreads();
+  s3 = block_sum(s3, red);
+  const float a = coef[0] / sqrtf(s1 / (float)F + eps), b = coef[1] / sqrtf(s2 / (float)F + eps),
+              c3 = coef[2] / sqrtf(s3 / (float)F + eps), e = coef[3];
+  for (int c = threadIdx.x; c < F; c += blockDim.x) {
+    const float z = to_f32<T>(x[base + c]) + (bias ? to_f32<T>(bias[c]) : 0.f);
+    out[base + c] = from_f32<T>(((c3 * z + b) * z + a) * z + e);
+  }
+}
+
+}  // namespace seqmix
+}  // namespace sxb
+
+/* decay fp32 [n_tokens, H * n] = exp(-exp(A_log[h]) * softplus(a_raw + dt_bias)) per head and key channel, beta fp32
+ * [n_tokens, H] = sigmoid(b_raw); a_raw `dtype` rows of pitch lda (H * n channels), b_raw `dtype` rows of pitch ldb (H),
+ * A_log fp32 [H], dt_bias fp32 [H * n]. */
+SXB_API int sxb_channel_decay_gates(const void* a_raw, long long lda, const void* b_raw, long long ldb, const void* A_log,
+                                    const void* dt_bias, void* decay, void* beta, int n_tokens, int H, int n, int dtype,
+                                    void* stream) {
+  const long long total = (long long)n_tokens * H * n;
+  if (total <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (channel_decay_gates_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)a_raw, lda, (const T*)b_raw, ldb, (const float*)A_log, (const float*)dt_bias,
+                             (float*)decay, (float*)beta, H, n, total)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* In place: x `dtype` [rows, width] *= sigmoid(gate[row, c / group]); gate `dtype` rows of pitch ldg with width / group
+ * entries (group 1: a gate per channel; group = head size: a gate per head). */
+SXB_API int sxb_sigmoid_gate_rows(void* x, const void* gate, long long ldg, long long rows, int width, int group,
+                                  int dtype, void* stream) {
+  const long long total = rows * width;
+  if (total <= 0) return SXB_OK;
+  if (group <= 0 || width % group) return SXB_ERR_BAD_ARG;
+  const int per = dtype == 0 ? 4 : 8;
+  const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && width % per == 0 &&
+                       (group == 1 ? (ldg % per == 0 && (reinterpret_cast<uintptr_t>(gate) & 15) == 0) : group % per == 0);
+  if (aligned) {
+    const long long nv = total / per;
+    if (dtype == 0) {
+      sigmoid_gate_rows_vec_kernel<float, 4><<<(unsigned)((nv + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+          (float*)x, (const float*)gate, ldg, nv, width / 4, group);
+    } else if (dtype == 2) {
+      sigmoid_gate_rows_vec_kernel<__nv_bfloat16, 8><<<(unsigned)((nv + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+          (__nv_bfloat16*)x, (const __nv_bfloat16*)gate, ldg, nv, width / 8, group);
+    } else {
+      return SXB_ERR_UNSUPPORTED;
+    }
+    SXB_CHECK_LAUNCH();
+    return SXB_OK;
+  }
+  SEQMIX_DISPATCH(dtype, (sigmoid_gate_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+                             (T*)x, (const T*)gate, ldg, total, width, group)));
+  SXB_CHECK_LAUNCH();
+  return SXB_OK;
+}
+
+/* out `dtype` [rows, F]: z = in + bias; a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e with (a, b, c, e) = coef
+ * fp32 [4] and rms over the row (eps inside the root); bias `dtype` [F] or null. */
+SXB_API int sxb_power_norm_act(const void* in, const void* bias, const void* coef, void* out, long long rows, int F,
+                               float eps, int dtype, void* stream) {
+  if (rows <= 0 || F <= 0) return SXB_OK;
+  SEQMIX_DISPATCH(dtype, (power_norm_act_kernel<T><<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
+                             (const T*)in, (const T*)bias, (const float*)coef, (T*)out, F, eps)));
   SXB_CHECK_LAUNCH();
   return SXB_OK;
 }

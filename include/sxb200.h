@@ -450,7 +450,8 @@ int sxb_int_gemv(const void* x, const void* codes, const void* scale, const void
 int sxb_embed_sinusoid(const void* ids, const void* pos, const void* table, void* out, int n_tokens, int width,
                        float scale, float base, int dtype, void* stream);
 int sxb_resid_norm_step(void* resid, const void* y, const void* w_post, const void* extra, const void* w_pre,
-                        void* out, long long rows, int width, float eps, float mult, int dtype, void* stream);
+                        void* out, long long rows, int width, float eps, float mult, int dtype,
+                        const void* y_scale, float w_add, void* stream);
 int sxb_qk_norm_append(const void* qkv, long long ld, const void* bias, void* q_out, void* kcache, void* vcache,
                        const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens, int max_blocks,
                        int block_size, int Hq, int G, int d, int dv, float eps, int normalize, int dtype,
@@ -472,10 +473,12 @@ int sxb_recurrence_gates(const void* a_raw, const void* b_raw, long long ld, con
                          void* stream);
 int sxb_linear_recurrence(const void* kvec, const void* qvec, long long ldkq, const void* val, long long ldv,
                           const void* decay, const void* beta, const void* skip, void* state, void* out,
-                          const void* seq_info, int n_seqs, int H, int G, int n, int dv, int delta, void* stream);
+                          const void* seq_info, int n_seqs, int H, int G, int n, int dv, int delta,
+                          int decay_channels, void* stream);
 int sxb_group_norm_gate(const void* y, const void* gate, long long ldg, const void* w, int wlen, void* out,
                         int n_tokens, int C, int gs, float eps, int gate_first, int dtype, void* stream);
-int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act, int dtype, void* stream);
+int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act, int dtype, float limit,
+                       void* stream);
 
 /* ---- csrc/seq_mixers.cu */
 int sxb_sink_attention_atoms(const void* q, const void* kcache, const void* vcache, const void* sink, void* out,
@@ -507,7 +510,7 @@ int sxb_latent_qk_prepare(const void* qfull, long long ldq, const void* qabs, lo
                           const void* kv, long long ldkv, const void* w_norm, const void* inv_freq, void* q_out,
                           void* cache, const void* tok_seq, const void* tok_pos, const void* tables, int n_tokens,
                           int max_blocks, int block_size, int H, int dim, int rot, int r, int rot_dims, float eps,
-                          int dtype, void* stream);
+                          int dtype, float amp, void* stream);
 int sxb_mlstm_prepare(const void* proj, long long ld, void* buf, int n_tokens, int H, int n, int dv, float qscale,
                       int dtype, void* stream);
 int sxb_mlstm_gate_scan(const void* raw_i, const void* raw_f, long long ld, const void* bias_i, const void* bias_f,
@@ -532,6 +535,28 @@ int sxb_row_gate_add(void* acc, const void* y, const void* gate, long long gate_
 /* ---- csrc/seq_mixers.cu */
 int sxb_router_logits(const void* x, long long ld, const void* w, const void* bias, void* out, int n_tokens,
                       int width, int R, int dtype, void* stream);
+
+/* ---- csrc/moe_ragged.cu */
+/* Group-limited gating with a choice correction.  logits fp32 [T, E]; correction fp32 [E] or null; the E experts form
+ * n_groups equal groups of neighbours of which the keep_groups whose best (score + correction) is largest stay eligible;
+ * the top_k largest (score + correction) among them win; scores fp32 [T, K] = softmax score of the winner / (sum of the
+ * winners' scores + 1e-20) * scale; assignments / offsets / expert_counts as sxb_top_k_gating. */
+int sxb_grouped_top_k_gating(const void* logits, const void* correction, void* scores, void* assignments,
+                             void* offsets, void* expert_counts, int n_tokens, int n_experts, int top_k,
+                             int n_groups, int keep_groups, float scale, void* stream);
+/* dst rows [offsets[g_lo], offsets[g_hi]) <- src rows of the same range; rows of row_bytes (a multiple of 16) bytes,
+ * offsets int32 on the device (group row offsets of an expert-sorted buffer), max_rows bounds the grid. */
+int sxb_copy_group_rows(const void* src, void* dst, const void* offsets, int g_lo, int g_hi, int row_bytes,
+                        long long max_rows, void* stream);
+
+/* ---- csrc/seq_mixers.cu */
+int sxb_channel_decay_gates(const void* a_raw, long long lda, const void* b_raw, long long ldb, const void* A_log,
+                            const void* dt_bias, void* decay, void* beta, int n_tokens, int H, int n, int dtype,
+                            void* stream);
+int sxb_sigmoid_gate_rows(void* x, const void* gate, long long ldg, long long rows, int width, int group,
+                          int dtype, void* stream);
+int sxb_power_norm_act(const void* in, const void* bias, const void* coef, void* out, long long rows, int F,
+                       float eps, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

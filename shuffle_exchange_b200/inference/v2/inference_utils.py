@@ -63,13 +63,14 @@ class ActivationType(IntEnum):
     SiGLU = 5
     IDENTITY = 6
     RELU_SQ = 7          # relu(x) ** 2
+    CLAMPED_SWIGLU = 8   # gated: g = min(gate, limit), u = clamp(up, -limit, limit); g * sigmoid(1.702 g) * (u + 1)
     InvalidType = -1
 
 
 def is_gated(act_fn: ActivationType) -> bool:
     if not isinstance(act_fn, ActivationType):
         act_fn = ActivationType(act_fn)
-    return act_fn in (ActivationType.GEGLU, ActivationType.ReGLU, ActivationType.SiGLU)
+    return act_fn in (ActivationType.GEGLU, ActivationType.ReGLU, ActivationType.SiGLU, ActivationType.CLAMPED_SWIGLU)
 
 
 def ceil_div(a: int, b: int) -> int:

@@ -18,7 +18,7 @@ from ....native import lib as _lib
 
 _lib.register({
     "sxb_embed_sinusoid": "pppp" "ii" "ff" "i" "p",
-    "sxb_resid_norm_step": "pppppp" "l" "i" "ff" "i" "p",
+    "sxb_resid_norm_step": "pppppp" "l" "i" "ff" "i" "p" "f" "p",
     "sxb_qk_norm_append": "p" "l" "ppppppp" "iiiiiii" "f" "ii" "p",
     "sxb_qkv_filter_norm_append": "p" "l" "ppppppppppp" "iiiiiiii" "f" "i" "f" "i" "i" "p",
     "sxb_sink_attention": "pppppppp" "iiiiiii" "f" "iiii" "p" "i" "p" "l" "i" "p",
@@ -27,15 +27,15 @@ _lib.register({
     "sxb_conv_state_update": "p" "l" "pp" "iii" "i" "p",
     "sxb_unit_norm_heads": "p" "l" "iii" "ff" "i" "p",
     "sxb_recurrence_gates": "pp" "l" "pppp" "iii" "i" "p",
-    "sxb_linear_recurrence": "pp" "l" "p" "l" "pppppp" "iiiiii" "p",
+    "sxb_linear_recurrence": "pp" "l" "p" "l" "pppppp" "iiiiii" "i" "p",
     "sxb_group_norm_gate": "pp" "l" "p" "i" "p" "iii" "f" "i" "i" "p",
-    "sxb_gated_act_rows": "pp" "l" "ii" "i" "p",
+    "sxb_gated_act_rows": "pp" "l" "ii" "i" "f" "p",
     "sxb_conv_residual": "pppppp" "iii" "i" "p",
     "sxb_post_norm_mix": "pppppp" "l" "i" "pp" "l" "i" "f" "i" "p",
     "sxb_rms_scale_rows": "pppp" "ii" "f" "i" "p",
     "sxb_rms_norm_slice": "p" "l" "pp" "ii" "f" "i" "p",
     "sxb_bias_act_rows": "ppp" "l" "ii" "i" "p",
-    "sxb_latent_qk_prepare": "p" "l" "p" "ll" "p" "l" "ppppppp" "iii" "iiiii" "f" "i" "p",
+    "sxb_latent_qk_prepare": "p" "l" "p" "ll" "p" "l" "ppppppp" "iii" "iiiii" "f" "i" "f" "p",
     "sxb_mlstm_prepare": "p" "l" "p" "iiii" "f" "i" "p",
     "sxb_mlstm_gate_scan": "pp" "l" "pp" "f" "ppppp" "iii" "i" "p",
     "sxb_mlstm_output": "ppp" "l" "pp" "iii" "f" "i" "p",
@@ -43,9 +43,12 @@ _lib.register({
     "sxb_scale_softcap": "p" "l" "ff" "p",
     "sxb_row_gate_add": "ppp" "l" "l" "i" "i" "p",
     "sxb_router_logits": "p" "l" "ppp" "iii" "i" "p",
+    "sxb_channel_decay_gates": "p" "l" "p" "l" "pppp" "iii" "i" "p",
+    "sxb_sigmoid_gate_rows": "pp" "l" "l" "ii" "i" "p",
+    "sxb_power_norm_act": "pppp" "l" "i" "f" "i" "p",
 })
 
-_ACTS = {"identity": 0, "relu": 1, "gelu": 2, "silu": 3, "relu_sq": 4}
+_ACTS = {"identity": 0, "relu": 1, "gelu": 2, "silu": 3, "relu_sq": 4, "clamped_swish": 5}
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -86,24 +89,30 @@ def _rms(x: torch.Tensor, eps: float) -> torch.Tensor:
 
 def resid_norm_step(resid: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[torch.Tensor],
                     extra: Optional[torch.Tensor], w_pre: Optional[torch.Tensor], eps: float,
-                    out_dtype: torch.dtype, mult: float = 1.0, copy_out: bool = False) -> Optional[torch.Tensor]:
+                    out_dtype: torch.dtype, mult: float = 1.0, copy_out: bool = False,
+                    y_scale: Optional[torch.Tensor] = None, w_add: float = 0.0) -> Optional[torch.Tensor]:
     """In place on the fp32 residual ``[T, W]``: ``+= mult * rms_norm(y) * w_post`` (if ``y``; without ``w_post``:
-    ``+= mult * y``), ``+= extra`` (if given); returns ``rms_norm(residual) * w_pre`` in ``out_dtype`` (without ``w_pre``:
-    the residual itself in ``out_dtype`` if ``copy_out``, else None).  One pass per row."""
+    ``+= mult * y``; with ``y_scale`` ``[W]`` the addend is also scaled per channel), ``+= extra`` (if given); returns
+    ``rms_norm(residual) * (w_add + w_pre)`` in ``out_dtype`` (``w_add = 1`` for weights stored as their distance from
+    one; without ``w_pre``: the residual itself in ``out_dtype`` if ``copy_out``, else None).  One pass per row."""
     T, W = resid.shape
     if resid.is_cuda:
         out = torch.empty(T, W, dtype=out_dtype, device=resid.device) if (w_pre is not None or copy_out) else None
         code = _lib.dtype_code(out_dtype)
+        if y_scale is not None and y_scale.dtype != out_dtype:
+            raise ValueError("the channel scale is stored in the activation dtype")
         _lib.call("sxb_resid_norm_step", resid.data_ptr(), _lib.ptr(y), _lib.ptr(w_post), _lib.ptr(extra),
-                  _lib.ptr(w_pre), _lib.ptr(out), T, W, float(eps), float(mult), code, _lib.stream_ptr())
+                  _lib.ptr(w_pre), _lib.ptr(out), T, W, float(eps), float(mult), code, _lib.ptr(y_scale), float(w_add),
+                  _lib.stream_ptr())
         return out
     if y is not None:
-        resid += mult * (_rms(y.float(), eps) * w_post.float() if w_post is not None else y.float())
+        add = mult * (_rms(y.float(), eps) * w_post.float() if w_post is not None else y.float())
+        resid += add * y_scale.float() if y_scale is not None else add
     if extra is not None:
         resid += extra
     if w_pre is None:
         return resid.to(out_dtype) if copy_out else None
-    return (_rms(resid, eps) * w_pre.float()).to(out_dtype)
+    return (_rms(resid, eps) * (w_add + w_pre.float())).to(out_dtype)
 
 
 # ------------------------------------------------------------------------------------------------ attention
@@ -358,22 +367,47 @@ def recurrence_gates(a_raw: torch.Tensor, b_raw: Optional[torch.Tensor], A_log: 
     return decay, beta
 
 
+def channel_decay_gates(a_raw: torch.Tensor, b_raw: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
+                        H: int, n: int):
+    """fp32 ``(decay [T, H*n], beta [T, H])`` of a delta rule whose decay differs per key channel: ``decay[t, h, c] =
+    exp(-exp(A_log[h]) * softplus(a_raw[t, h*n + c] + dt_bias[h*n + c]))``, ``beta = sigmoid(b_raw)``.  ``a_raw``
+    ``[T, H*n]`` and ``b_raw`` ``[T, H]`` may be column slices; ``A_log`` fp32 ``[H]``, ``dt_bias`` fp32 ``[H*n]``."""
+    T = a_raw.shape[0]
+    if a_raw.is_cuda:
+        decay = torch.empty(T, H * n, dtype=torch.float32, device=a_raw.device)
+        beta = torch.empty(T, H, dtype=torch.float32, device=a_raw.device)
+        if b_raw.dtype != a_raw.dtype:
+            raise ValueError("a_raw and b_raw share their dtype")
+        _lib.call("sxb_channel_decay_gates", _rows(a_raw).data_ptr(), a_raw.stride(0), _rows(b_raw).data_ptr(),
+                  b_raw.stride(0), A_log.data_ptr(), dt_bias.data_ptr(), decay.data_ptr(), beta.data_ptr(), T, H, n,
+                  _dt(a_raw), _lib.stream_ptr())
+        return decay, beta
+    dt = torch.nn.functional.softplus(a_raw.float() + dt_bias.float(), threshold=30.0)
+    decay = torch.exp(-torch.exp(A_log.float()).repeat_interleave(n)[None, :] * dt)
+    return decay, torch.sigmoid(b_raw.float())
+
+
 def linear_recurrence(kvec: torch.Tensor, qvec: torch.Tensor, val: torch.Tensor, decay: torch.Tensor,
                       beta: torch.Tensor, skip: Optional[torch.Tensor], state: torch.Tensor, seq_info: torch.Tensor,
                       H: int, G: int, n: int, dv: int, delta: bool) -> torch.Tensor:
     """Per sequence and head, rows in order: ``S <- decay S``; ``u = beta (v - S^T k)`` (``delta``) or ``beta v``;
     ``S <- S + k u^T``; ``o = S^T q (+ skip[h] v)``.  ``kvec`` / ``qvec`` fp32 ``[T, G*n]`` and ``val`` fp32
     ``[T, H*dv]`` may be column slices (``kvec`` and ``qvec`` with one row pitch); ``state`` fp32 ``[slots, H, dv, n]`` is
-    read (zero for a sequence that has seen no token) and written back.  Returns fp32 ``[T, H*dv]``."""
+    read (zero for a sequence that has seen no token) and written back.  ``decay`` fp32 ``[T, H]`` is one factor per
+    head; ``[T, H*n]`` one per head and key channel (it multiplies the state's entries of that channel).  Returns fp32
+    ``[T, H*dv]``."""
     T = val.shape[0]
+    per_channel = decay.shape[1] == H * n and n > 1
     if val.is_cuda:
         if kvec.stride(0) != qvec.stride(0):
             raise ValueError("kvec and qvec must share their row pitch")
+        if not decay.is_contiguous() or decay.shape[1] not in (H, H * n):
+            raise ValueError("decay is a contiguous [T, H] or [T, H*n] tensor")
         out = torch.empty(T, H * dv, dtype=torch.float32, device=val.device)
         _lib.call("sxb_linear_recurrence", _rows(kvec).data_ptr(), _rows(qvec).data_ptr(), kvec.stride(0),
                   _rows(val).data_ptr(), val.stride(0), decay.data_ptr(), beta.data_ptr(), _lib.ptr(skip),
                   state.data_ptr(), out.data_ptr(), seq_info.data_ptr(), seq_info.shape[0], H, G, n, dv, int(delta),
-                  _lib.stream_ptr())
+                  int(per_channel), _lib.stream_ptr())
         return out
     out = torch.empty(T, H, dv, dtype=torch.float32)
     rep = H // G
@@ -383,7 +417,7 @@ def linear_recurrence(kvec: torch.Tensor, qvec: torch.Tensor, val: torch.Tensor,
             k = kvec[t].reshape(G, n).repeat_interleave(rep, dim=0)                      # [H, n]
             q = qvec[t].reshape(G, n).repeat_interleave(rep, dim=0)
             v = val[t].reshape(H, dv)
-            S = S * decay[t][:, None, None]
+            S = S * (decay[t].reshape(H, 1, n) if per_channel else decay[t][:, None, None])
             u = beta[t][:, None] * ((v - torch.einsum("hvn,hn->hv", S, k)) if delta else v)
             S = S + u[:, :, None] * k[:, None, :]
             o = torch.einsum("hvn,hn->hv", S, q)
@@ -395,34 +429,39 @@ def linear_recurrence(kvec: torch.Tensor, qvec: torch.Tensor, val: torch.Tensor,
 
 
 def group_norm_gate(y: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, group_size: int, eps: float,
-                    gate_first: bool, out_dtype: torch.dtype) -> torch.Tensor:
+                    gate_first: bool, out_dtype: torch.dtype, sigmoid: bool = False) -> torch.Tensor:
     """RMS norm over groups of ``group_size`` channels of fp32 ``y`` ``[T, C]`` with a SiLU gate ``[T, C]`` (column slice
     allowed) and a weight that repeats along the row.  ``gate_first``: ``norm(y * silu(gate)) * w``; else
-    ``norm(y) * w * silu(gate)``."""
+    ``norm(y) * w * silu(gate)``.  ``sigmoid``: the gate is ``sigmoid(gate)`` instead of ``silu(gate)``."""
     T, C = y.shape
     if y.is_cuda:
         out = torch.empty(T, C, dtype=out_dtype, device=y.device)
         _lib.call("sxb_group_norm_gate", y.data_ptr(), _rows(gate).data_ptr(), gate.stride(0), w.data_ptr(), w.numel(),
-                  out.data_ptr(), T, C, group_size, float(eps), int(gate_first), _lib.dtype_code(out_dtype),
-                  _lib.stream_ptr())
+                  out.data_ptr(), T, C, group_size, float(eps), int(gate_first) | (2 if sigmoid else 0),
+                  _lib.dtype_code(out_dtype), _lib.stream_ptr())
         return out
-    sg = torch.nn.functional.silu(gate.float())
+    sg = torch.sigmoid(gate.float()) if sigmoid else torch.nn.functional.silu(gate.float())
     wf = w.float().repeat(C // w.numel())
     z = y * sg if gate_first else y
     z = _rms(z.reshape(T, C // group_size, group_size), eps).reshape(T, C) * wf
     return (z if gate_first else z * sg).to(out_dtype)
 
 
-def gated_act_rows(x: torch.Tensor, act: str = "gelu") -> torch.Tensor:
-    """``act(x[:, :F]) * x[:, F:]`` for rows of any width, bf16 or fp32 (``gelu`` is the tanh form)."""
+def gated_act_rows(x: torch.Tensor, act: str = "gelu", limit: float = 0.0) -> torch.Tensor:
+    """``act(x[:, :F]) * x[:, F:]`` for rows of any width, bf16 or fp32 (``gelu`` is the tanh form).  ``clamped_swish``:
+    ``g = min(x[:, :F], limit)``, ``u = clamp(x[:, F:], -limit, limit)``, result ``g * sigmoid(1.702 g) * (u + 1)``."""
     T, F2 = x.shape
     Fh = F2 // 2
     if x.is_cuda:
         x = x.contiguous()
         out = torch.empty(T, Fh, dtype=x.dtype, device=x.device)
-        _lib.call("sxb_gated_act_rows", x.data_ptr(), out.data_ptr(), T, Fh, _ACTS[act], _dt(x), _lib.stream_ptr())
+        _lib.call("sxb_gated_act_rows", x.data_ptr(), out.data_ptr(), T, Fh, _ACTS[act], _dt(x), float(limit),
+                  _lib.stream_ptr())
         return out
     g, u = x[:, :Fh].float(), x[:, Fh:].float()
+    if act == "clamped_swish":
+        g, u = g.clamp(max=limit), u.clamp(min=-limit, max=limit)
+        return (g * torch.sigmoid(1.702 * g) * (u + 1.0)).to(x.dtype)
     a = {"gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"), "silu": torch.nn.functional.silu,
          "relu": torch.relu, "identity": lambda t: t}[act](g)
     return (a * u).to(x.dtype)
@@ -441,6 +480,39 @@ def bias_act_rows(x: torch.Tensor, bias: Optional[torch.Tensor], act: str) -> to
     a = {"gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"), "silu": torch.nn.functional.silu,
          "relu": torch.relu, "identity": lambda t: t, "relu_sq": lambda t: torch.relu(t) ** 2}[act](z)
     return a.to(x.dtype)
+
+
+def power_norm_act(x: torch.Tensor, bias: Optional[torch.Tensor], coef: torch.Tensor, eps: float) -> torch.Tensor:
+    """Three-power normalised activation of every row: ``z = x + bias``; ``a z / rms(z) + b z^2 / rms(z^2) + c z^3 /
+    rms(z^3) + e`` with ``(a, b, c, e) = coef`` (fp32 ``[4]``) and ``rms(u) = sqrt(mean(u^2) + eps)`` over the row; the
+    sums are 32-bit, input and output share their dtype (bf16 or fp32)."""
+    T, Fw = x.shape
+    if x.is_cuda:
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        if coef.dtype != torch.float32 or coef.numel() != 4:
+            raise ValueError("coef is an fp32 tensor of four numbers")
+        _lib.call("sxb_power_norm_act", x.data_ptr(), _lib.ptr(bias), coef.data_ptr(), out.data_ptr(), T, Fw, float(eps),
+                  _dt(x), _lib.stream_ptr())
+        return out
+    z = x.float() + (bias.float() if bias is not None else 0.0)
+    c = coef.float()
+    return (c[0] * _rms(z, eps) + c[1] * _rms(z * z, eps) + c[2] * _rms(z * z * z, eps) + c[3]).to(x.dtype)
+
+
+def sigmoid_gate_rows_(x: torch.Tensor, gate: torch.Tensor, group: int = 1) -> torch.Tensor:
+    """In place: ``x[t, c] *= sigmoid(gate[t, c // group])``; ``gate`` ``[T, W / group]`` (a column slice is fine) has one
+    entry per channel (``group = 1``) or per run of ``group`` channels (a head)."""
+    T, W = x.shape
+    if x.is_cuda:
+        if not x.is_contiguous() or gate.dtype != x.dtype:
+            raise ValueError("expected contiguous rows and a gate of the same dtype")
+        _lib.call("sxb_sigmoid_gate_rows", x.data_ptr(), _rows(gate).data_ptr(), gate.stride(0), T, W, int(group),
+                  _dt(x), _lib.stream_ptr())
+        return x
+    g = torch.sigmoid(gate[:, : W // group].float()).repeat_interleave(group, dim=1)
+    x.copy_((x.float() * g).to(x.dtype))
+    return x
 
 
 # ------------------------------------------------------------------------------------------------ post-norm layers
@@ -521,12 +593,13 @@ def rms_norm_slice(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor
 
 
 # ------------------------------------------------------------------------------------------------ latent attention
-def _rope_pairs(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
-    """Rotate the pairs (2i, 2i+1), i < len(inv_freq), of the last axis of fp32 ``x`` ``[T, ..., n]`` by ``pos * inv_freq``."""
+def _rope_pairs(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, amp: float = 1.0) -> torch.Tensor:
+    """Rotate the pairs (2i, 2i+1), i < len(inv_freq), of the last axis of fp32 ``x`` ``[T, ..., n]`` by ``pos * inv_freq``
+    (cos and sin times ``amp``)."""
     nd = 2 * inv_freq.numel()
     ang = pos.float()[:, None] * inv_freq.float()[None, :]
     shape = (x.shape[0],) + (1,) * (x.dim() - 2) + (nd // 2,)
-    cs, sn = ang.cos().view(shape), ang.sin().view(shape)
+    cs, sn = (ang.cos() * amp).view(shape), (ang.sin() * amp).view(shape)
     out = x.clone()
     u, v = x[..., 0:nd:2], x[..., 1:nd:2]
     out[..., 0:nd:2] = u * cs - v * sn
@@ -536,12 +609,13 @@ def _rope_pairs(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> t
 
 def latent_qk_prepare(q: torch.Tensor, q_abs: torch.Tensor, kv: torch.Tensor, w_norm: torch.Tensor,
                       inv_freq: torch.Tensor, cache: torch.Tensor, tok_seq: torch.Tensor, tok_pos: torch.Tensor,
-                      tables: torch.Tensor, H: int, dim: int, rot: int, eps: float) -> torch.Tensor:
+                      tables: torch.Tensor, H: int, dim: int, rot: int, eps: float, amp: float = 1.0) -> torch.Tensor:
     """Latent attention, per token.  ``kv`` ``[T, r + rot]``: ``cache[page, offset, 0] = [kv[:r] / rms * w_norm |
     rope(kv[r:])]`` (``cache`` ``[pages, block, 1, r + rot]``).  ``q`` ``[T, H * (dim + rot)]`` (heads laid out
     ``[dim unrotated | rot rotated]``) and ``q_abs`` ``[T, H, r]`` (any strides with unit inner stride; the unrotated
     part of every query head carried through the key up-projection): returns fp32 ``[T, H, r + rot] = [q_abs |
-    rope(q[..., dim:])]``.  ``rope`` turns the pairs ``(2i, 2i+1)``, ``i < len(inv_freq)``, by ``pos * inv_freq[i]``."""
+    rope(q[..., dim:])]``.  ``rope`` turns the pairs ``(2i, 2i+1)``, ``i < len(inv_freq)``, by ``pos * inv_freq[i]`` and
+    multiplies the turned channels by ``amp``."""
     T = q.shape[0]
     r = kv.shape[1] - rot
     bs = cache.shape[1]
@@ -550,14 +624,15 @@ def latent_qk_prepare(q: torch.Tensor, q_abs: torch.Tensor, kv: torch.Tensor, w_
         _lib.call("sxb_latent_qk_prepare", _rows(q).data_ptr(), q.stride(0), _rows(q_abs).data_ptr(), q_abs.stride(0),
                   q_abs.stride(1), _rows(kv).data_ptr(), kv.stride(0), w_norm.data_ptr(), inv_freq.data_ptr(),
                   out.data_ptr(), cache.data_ptr(), tok_seq.data_ptr(), tok_pos.data_ptr(), tables.data_ptr(), T,
-                  tables.shape[1], bs, H, dim, rot, r, 2 * inv_freq.numel(), float(eps), _dt(q), _lib.stream_ptr())
+                  tables.shape[1], bs, H, dim, rot, r, 2 * inv_freq.numel(), float(eps), _dt(q), float(amp),
+                  _lib.stream_ptr())
         return out
     c = (_rms(kv[:, :r].float(), eps) * w_norm.float()).to(cache.dtype)
-    kr = _rope_pairs(kv[:, r:].float(), tok_pos, inv_freq).to(cache.dtype)
+    kr = _rope_pairs(kv[:, r:].float(), tok_pos, inv_freq, amp).to(cache.dtype)
     page = tables[tok_seq.long(), (tok_pos // bs).long()].long()
     off = (tok_pos % bs).long()
     cache[page, off, 0] = torch.cat([c, kr], dim=1)
-    qr = _rope_pairs(q.reshape(T, H, dim + rot)[:, :, dim:].float(), tok_pos, inv_freq)
+    qr = _rope_pairs(q.reshape(T, H, dim + rot)[:, :, dim:].float(), tok_pos, inv_freq, amp)
     return torch.cat([q_abs.float(), qr], dim=2).contiguous()
 
 

@@ -1,14 +1,17 @@
 """Ragged-batch model for hybrid layer stacks: every layer names its own token mixer — attention over the paged cache
-(per-head keys and values, or one latent vector per token), a gated-delta-rule, state-space-duality or matrix-memory
-LSTM recurrence — and may or may not have a feed-forward (gated, biased, or a mixture of experts); a span of layers can
-be executed several times in a row with the same weights, every execution with its own cache or state.
+(per-head keys and values, or one latent vector per token), a gated-delta-rule (one decay per head, or per head and
+key channel), state-space-duality or matrix-memory LSTM recurrence — and may or may not have a feed-forward (gated,
+biased, or a mixture of experts); a span of layers can be executed several times in a row with the same weights, and
+single layers can borrow another layer's weights, every execution with its own cache or state.
 
 The stack is data (:class:`HybridSpec`), as :class:`~.inference_transformer_base.ArchSpec` is for the uniform
 transformer family; per-architecture policies (``fomalix/policy.py``) fill it from a checkpoint's configuration and fuse
 the checkpoint's tensors into the projection layouts the mixer modules declare.
 
 Three layer forms (``HybridSpec.block_form``).  ``"sandwich"``: ``x += post_norm(sublayer(pre_norm(x)))``.
-``"pre_scaled"``: ``x += m * sublayer(pre_norm(x))`` with one multiplier ``m`` for the whole stack, and optionally a
+``"pre_scaled"``: ``x += m * sublayer(pre_norm(x))`` with one multiplier ``m`` for the whole stack (with ``layer_scale``
+also a learned scale per layer, sublayer and channel: ``x += m * ls (.) sublayer(pre_norm(x))``; with
+``norm_weight_offset`` the norms multiply by ``offset + w``), and optionally a
 per-layer token input behind the feed-forward: ``x += m * rms_norm(proj(gelu(gate x) * e))`` where ``e`` is the layer's
 part of one more embedding row of the token (``token_side_dim`` channels per layer).
 ``"post_scaled"``: ``x += scale (.) post_norm(sublayer(x + conv(x)))`` -- no pre-norm, a post-norm with one gain, a
@@ -36,7 +39,7 @@ from ..kernels import mixer_ops as M
 from ..modules import heuristics
 from ..modules.configs import (DSEmbeddingsConfig, DSLinearConfig, DSMoEConfig, DSNormConfig, DSRecurrentMixerConfig,
                                DSSelfAttentionConfig, DistanceBiasConfig, MaskingType, PositionalEmbeddingType,
-                               RotateHalfConfig)
+                               RotaryScalingConfig, RotateHalfConfig)
 from ..ragged.kv_cache import KVCacheConfig
 from ..ragged.state_pool import StatePoolConfig
 from .inference_transformer_base import DSInferenceModelBase, LayerWeights
@@ -44,7 +47,7 @@ from .inference_transformer_base import DSInferenceModelBase, LayerWeights
 
 @dataclass
 class HybridLayerSpec:
-    kind: str                                   # "attention" | "latent_attention" | "delta" | "ssd" | "mlstm"
+    kind: str                      # "attention" | "latent_attention" | "delta" | "channel_delta" | "ssd" | "mlstm"
     n_heads: int
     n_heads_kv: int                             # key/value heads (attention), key/query heads (delta), groups (ssd)
     key_dim: int                                # query/key head size, or state size per group (ssd)
@@ -82,6 +85,19 @@ class HybridLayerSpec:
     ff_gated: bool = True                       # moe: experts are down(act(gate) * up); False: down(act(up))
     router_bias: bool = False
     shared_ff_dim: int = 0                      # moe: a shared expert of this width, gated by a sigmoid per token
+    # latent attention: queries straight from the input (no query latent), one gate per head instead of one per output
+    # channel (``out_gate``), wavelength-dependent slowing of the rotation (factor, original context, fast, slow turns)
+    q_direct: bool = False
+    gate_per_head: bool = False
+    rot_scaling: Optional[Tuple[float, float, float, float]] = None
+    # moe: group-limited choice by score + correction, weights rescaled, identity experts behind the real ones, clamp of
+    # the experts' gated activation
+    moe_correction: bool = False
+    moe_groups: int = 1
+    moe_keep_groups: int = 1
+    moe_scale: float = 1.0
+    moe_identity: int = 0
+    ff_limit: float = 0.0
 
 
 @dataclass
@@ -100,6 +116,8 @@ class HybridSpec:
     block_form: str = "sandwich"                # "sandwich" | "post_scaled" | "pre_scaled"
     residual_mult: float = 1.0                  # pre_scaled: what every sublayer's output is multiplied by
     token_side_dim: int = 0                     # pre_scaled: channels per layer of the per-layer token input (0: none)
+    layer_scale: bool = False                   # pre_scaled: every sublayer's output times a per-channel ``ls1`` / ``ls2``
+    norm_weight_offset: float = 0.0             # pre_scaled: norm weights are ``offset + w`` (1: stored around zero)
     logit_scale: float = 1.0
     logit_softcap: float = 0.0                  # > 0: logits <- cap * tanh(logits / cap)
     input_conv_taps: int = 0                    # post_scaled: taps of the filter in front of every sublayer
@@ -183,12 +201,15 @@ class DSHybridModel(DSInferenceModelBase):
                     max_tokens=mt, model_dim=s.model_dim, intermediate_features=L.ff_dim, n_experts=L.n_experts,
                     top_k=L.top_k, input_dtype=dt, output_dtype=dt,
                     activation=({"silu": ActivationType.SiGLU, "gelu": ActivationType.GEGLU,
-                                 "relu": ActivationType.ReGLU} if L.ff_gated else
+                                 "relu": ActivationType.ReGLU,
+                                 "clamped_swish": ActivationType.CLAMPED_SWIGLU} if L.ff_gated else
                                 {"silu": ActivationType.SILU, "gelu": ActivationType.GELU, "relu": ActivationType.RELU,
                                  "relu_sq": ActivationType.RELU_SQ})[L.ff_activation],
                     normalize_scores=L.moe_renormalize,
                     score_function=L.moe_score, weight_input=L.moe_weight_input, router_dtype=DtypeEnum.fp32,
-                    router_bias=L.router_bias, shared_features=L.shared_ff_dim), ec)
+                    router_bias=L.router_bias, shared_features=L.shared_ff_dim,
+                    score_correction=L.moe_correction, n_groups=L.moe_groups, keep_groups=L.moe_keep_groups,
+                    score_scale=L.moe_scale, identity_experts=L.moe_identity, activation_limit=L.ff_limit), ec)
             self.moes.append(moe)
             if L.kind == "latent_attention":
                 mod = heuristics.instantiate_attention(DSSelfAttentionConfig(
@@ -200,7 +221,11 @@ class DSHybridModel(DSInferenceModelBase):
                     positional_embedding_type=(PositionalEmbeddingType.rotate_every_other if L.rot_dims > 0
                                                else PositionalEmbeddingType.none),
                     positional_embedding_config=RotateHalfConfig(theta_base=L.rot_base, rotate_dim=L.rot_dims),
-                    qk_norm_eps=s.norm_eps, sink=L.sink, kv_latent_dim=L.kv_rank, rope_head_dim=L.rot_dim), ec)
+                    qk_norm_eps=s.norm_eps, sink=L.sink, kv_latent_dim=L.kv_rank, rope_head_dim=L.rot_dim,
+                    output_gate=L.out_gate, output_gate_per_head=L.gate_per_head, q_direct=L.q_direct,
+                    rotary_scaling=None if L.rot_scaling is None else RotaryScalingConfig(
+                        factor=L.rot_scaling[0], original=L.rot_scaling[1], fast=L.rot_scaling[2],
+                        slow=L.rot_scaling[3])), ec)
             elif L.kind == "attention" and (L.conv_taps > 1 or L.qk_norm_weight or L.dist_rows > 0 or L.out_gate
                                             or L.q_temp_coef != 0.0):
                 mask = (MaskingType.chunked if L.chunk_size > 0 else
@@ -302,12 +327,18 @@ class DSHybridModel(DSInferenceModelBase):
     # ------------------------------------------------------------------------------------------ forward
     def _feed_forward(self, L: HybridLayerSpec, lw: LayerWeights, x: torch.Tensor, li: int = -1) -> torch.Tensor:
         if L.ff_kind == "moe":
+            if L.moe_correction or L.moe_identity > 0:
+                return self.moes[li](x, lw.moe_gate, lw.moe_w1, lw.moe_w2,
+                                     correction=lw.moe_correction if L.moe_correction else None)
             if L.router_bias or L.shared_ff_dim > 0:
                 return self.moes[li](x, lw.moe_gate, lw.moe_w1, lw.moe_w2, gate_b=lw.moe_gate_b if L.router_bias else None,
                                      shared=(lw.shared_up, lw.shared_down) if L.shared_ff_dim > 0 else None)
             return self.moes[li](x, lw.moe_gate, lw.moe_w1, lw.moe_w2)
         if L.ff_kind == "biased":
-            h = M.bias_act_rows(self.linear(x, lw.w_up), lw.b_up, L.ff_activation)
+            if L.ff_activation == "power_norm":
+                h = M.power_norm_act(self.linear(x, lw.w_up), lw.b_up, lw.act_coef, self.spec.norm_eps)
+            else:
+                h = M.bias_act_rows(self.linear(x, lw.w_up), lw.b_up, L.ff_activation)
             return F.linear(h, lw.w_down, lw.b_down)
         h = self.linear(x, lw.w_gate_up)
         if h.is_cuda and h.dtype == torch.bfloat16 and L.ff_dim % 8 == 0:
@@ -395,29 +426,30 @@ class DSHybridModel(DSInferenceModelBase):
         output of a sublayer is added by the kernel that also computes what the next sublayer reads (its norm, or the
         stream itself in the activation dtype for the token input), so ``y`` below is always one addition behind."""
         W, s = self.weights, self.spec
-        m = s.residual_mult
+        m, off = s.residual_mult, s.norm_weight_offset
         resid = self.embed(batch, W["embed"])
         first = resid.clone() if any(again for _, again in self._runs) else None
-        y = post = None                 # pending: resid += m * y (post None) or m * rms_norm(y) * post
+        y = post = ls = None            # pending: resid += m * ls (.) y (post None) or m * ls (.) rms_norm(y) * post
         for r, (li, again) in enumerate(self._runs):
             lw, L = W["layers"][li], s.layers[li]
-            _, x = self.norm(resid, y, lw.norm1, None, post, first if again else None, m)
-            y, post = self._mixer(r, li, lw, x, batch), None
+            _, x = self.norm(resid, y, lw.norm1, None, post, first if again else None, m, False, ls, off)
+            y, post, ls = self._mixer(r, li, lw, x, batch), None, lw.ls1 if s.layer_scale else None
             if L.ff_dim > 0:
-                _, x = self.norm(resid, y, lw.norm2, None, None, None, m)
-                y = self._feed_forward(L, lw, x, li)
+                _, x = self.norm(resid, y, lw.norm2, None, None, None, m, False, ls, off)
+                y, ls = self._feed_forward(L, lw, x, li), lw.ls2 if s.layer_scale else None
             if s.token_side_dim > 0:
-                _, x = self.norm(resid, y, None, None, None, None, m, copy_out=True)
-                y, post = self._token_side(li, lw, x, batch), lw.side_norm
+                _, x = self.norm(resid, y, None, None, None, None, m, True, ls)
+                y, post, ls = self._token_side(li, lw, x, batch), lw.side_norm, None
             if self.layer_outputs is not None:
-                self.norm(resid, y, None, None, post, None, m)
-                y = post = None
+                self.norm(resid, y, None, None, post, None, m, False, ls)
+                y = post = ls = None
                 self.layer_outputs.append(resid.clone())
         rows = batch.last_token_index().long()
         if rows.numel() == 0:               # a step that only advances caches and states
             return torch.empty(0, s.vocab_size, dtype=torch.float32, device=resid.device)
         resid = resid.index_select(0, rows)
-        _, x = self.norm(resid, None if y is None else y.index_select(0, rows), W["final_norm_w"], None, post, None, m)
+        _, x = self.norm(resid, None if y is None else y.index_select(0, rows), W["final_norm_w"], None, post, None, m,
+                         False, ls, off)
         logits = self.linear(x, W["unembed"])[:, : s.vocab_size].float().contiguous()
         if s.logit_scale != 1.0 or s.logit_softcap > 0.0:
             M.scale_softcap_(logits, s.logit_scale, s.logit_softcap)

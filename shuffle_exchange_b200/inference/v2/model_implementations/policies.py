@@ -275,7 +275,9 @@ CONTAINER_POLICIES = {"llama": Llama2ContainerPolicy, "mistral": Llama2Container
 from .fomalix import FomalixPolicy  # noqa: E402
 from .kekopel import KekopelPolicy  # noqa: E402
 from .ridazen import RidazenPolicy  # noqa: E402
+from .pifazen import PifazenPolicy  # noqa: E402
 
-POLICIES = {"fomalix": FomalixPolicy, "kekopel": KekopelPolicy, "ridazen": RidazenPolicy, "llama": Llama2Policy, "mistral": MistralPolicy, "mixtral": MixtralPolicy, "falcon": FalconPolicy,
+POLICIES = {"fomalix": FomalixPolicy, "kekopel": KekopelPolicy, "ridazen": RidazenPolicy, "pifazen": PifazenPolicy,
+            "llama": Llama2Policy, "mistral": MistralPolicy, "mixtral": MixtralPolicy, "falcon": FalconPolicy,
             "opt": OPTPolicy, "phi": PhiPolicy, "phi3": Phi3Policy, "qwen": QwenPolicy, "qwen2": Qwen2Policy,
             "qwen2_moe": Qwen2MoePolicy}

@@ -28,6 +28,17 @@ class RotateHalfConfig(DeepSpeedConfigModel):
     rotate_dim: Optional[int] = None      # None: rotate the whole head; < head_size: partial rotary (Phi, GPT-NeoX)
 
 
+class RotaryScalingConfig(DeepSpeedConfigModel):
+    """Frequency interpolation by wavelength for contexts ``factor`` times longer than ``original`` positions: pairs
+    that complete fewer than ``slow`` turns over the original context are slowed by ``factor``, pairs with more than
+    ``fast`` turns keep their frequency, the ones between are blended along a linear ramp over the pair index; cos and
+    sin are multiplied by ``0.1 ln(factor) + 1``."""
+    factor: float
+    original: float
+    fast: float = 32.0
+    slow: float = 1.0
+
+
 class MaskingType(Enum):
     none = "none"
     causal = "causal"
@@ -69,6 +80,11 @@ class DSSelfAttentionConfig(DSModuleConfig):
     q_temp_every: int = 1
     distance_bias: Optional[DistanceBiasConfig] = None      # with PositionalEmbeddingType.distance_bias
     output_gate: bool = False             # the heads' outputs are multiplied by sigmoid of one more projection
+    output_gate_per_head: bool = False    # that projection has one output per head instead of one per output channel
+    # Latent attention: the queries are projected straight from the input (``H (head_size + rope_head_dim)`` columns
+    # at the start of the fused projection) instead of through a normalised latent with an up-projection.
+    q_direct: bool = False
+    rotary_scaling: Optional[RotaryScalingConfig] = None
 
 
 class DSEmbeddingsConfig(DSModuleConfig):
@@ -107,6 +123,16 @@ class DSMoEConfig(DSModuleConfig):
     # A shared expert of ``shared_features`` channels runs for every token; its output is multiplied by the sigmoid of
     # one more router row (the row after the experts' rows) and added.
     shared_features: int = 0
+    # Group-limited choice: the router has ``n_experts + identity_experts`` outputs in ``n_groups`` equal groups of
+    # neighbours; the winners are the ``top_k`` largest ``score + correction`` inside the ``keep_groups`` groups whose
+    # best member is largest; the weights are the winners' plain scores / their sum * ``score_scale``.  The last
+    # ``identity_experts`` outputs stand for experts that return their input (they have no weights).
+    score_correction: bool = False
+    n_groups: int = 1
+    keep_groups: int = 1
+    score_scale: float = 1.0
+    identity_experts: int = 0
+    activation_limit: float = 0.0         # ActivationType.CLAMPED_SWIGLU: the clamp
 
 
 class DSNormConfig(DSModuleConfig):
@@ -131,7 +157,9 @@ class DSRecurrentMixerConfig(DSModuleConfig):
     """A token mixer that carries a matrix state per head instead of a key / value cache.
 
     ``kind`` ``"delta"``: gated delta rule (keys / queries of ``key_dim`` channels shared by ``n_heads // n_heads_kv``
-    value heads, short convolutions on q, k, v).  ``"ssd"``: state-space duality (B / C of ``key_dim`` = state size per
+    value heads, short convolutions on q, k, v).  ``"channel_delta"``: the same rule with one decay per head and key
+    channel (from a two-step projection), a sigmoid write strength and a sigmoid output gate from a second two-step
+    projection behind the per-head norm.  ``"ssd"``: state-space duality (B / C of ``key_dim`` = state size per
     group, a convolution over x | B | C, a skip term and a gated group norm).  ``"mlstm"``: matrix-memory LSTM
     (exponential input gate, sigmoid forget gate in log space, both capped by ``gate_cap``, a running maximum that
     keeps the exponentials in range, a normaliser state, per-head unit-RMS and a sigmoid output gate; no convolution)."""

@@ -66,9 +66,11 @@ def instantiate_unembed(unembed_config: DSUnembedConfig, engine_config: RaggedIn
 
 def instantiate_recurrent_mixer(mixer_config: DSRecurrentMixerConfig,
                                 engine_config: RaggedInferenceEngineConfig) -> DSRecurrentMixerBase:
-    name = {"delta": "gated_delta_mixer", "ssd": "ssd_mixer", "mlstm": "mlstm_mixer"}.get(mixer_config.kind)
+    name = {"delta": "gated_delta_mixer", "ssd": "ssd_mixer", "mlstm": "mlstm_mixer",
+            "channel_delta": "channel_delta_mixer"}.get(mixer_config.kind)
     if name is None:
-        raise ValueError(f"Unknown recurrent mixer kind {mixer_config.kind!r}; expected 'delta', 'ssd' or 'mlstm'")
+        raise ValueError(f"Unknown recurrent mixer kind {mixer_config.kind!r}; expected 'delta', 'channel_delta', 'ssd' "
+                         "or 'mlstm'")
     return DSRecurrentMixerRegistry.instantiate_config(ConfigBundle(name=name, config=mixer_config))
 
 

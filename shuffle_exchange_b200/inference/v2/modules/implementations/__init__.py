@@ -21,6 +21,8 @@
                               query temperature, learned distance-bucket bias on the scores, sigmoid output gate
  ``gated_delta_mixer`` / ``ssd_mixer``   short convolutions with carried inputs + linear recurrence with a matrix
                               state per (sequence slot, head) + gated group norm
+ ``channel_delta_mixer``      the delta rule with one decay per head and key channel and a sigmoid output gate, both
+                              from two-step projections
 =========================  =======================================================================================
 """
 from __future__ import annotations
@@ -52,15 +54,18 @@ def _dt(x) -> DtypeEnum:
 def _act_name(act: ActivationType) -> str:
     return {ActivationType.GELU: "gelu", ActivationType.RELU: "relu", ActivationType.SILU: "silu",
             ActivationType.GEGLU: "gelu", ActivationType.ReGLU: "relu", ActivationType.SiGLU: "silu",
-            ActivationType.IDENTITY: "identity", ActivationType.RELU_SQ: "relu_sq"}[ActivationType(act)]
+            ActivationType.IDENTITY: "identity", ActivationType.RELU_SQ: "relu_sq",
+            ActivationType.CLAMPED_SWIGLU: "clamped_swish"}[ActivationType(act)]
 
 
-def _apply_activation(y: torch.Tensor, bias: Optional[torch.Tensor], act: ActivationType) -> torch.Tensor:
+def _apply_activation(y: torch.Tensor, bias: Optional[torch.Tensor], act: ActivationType, limit: float = 0.0) -> torch.Tensor:
     act = ActivationType(act)
     if is_gated(act):
         # fused weights are [gate | up] halves (HF gate_proj / up_proj order): act(gate) * up
         if bias is not None:
             y = y + bias
+        if act == ActivationType.CLAMPED_SWIGLU:
+            return M.gated_act_rows(y, "clamped_swish", limit)
         if y.is_cuda and (y.dtype != torch.bfloat16 or (y.shape[-1] // 2) % 8):
             return M.gated_act_rows(y, _act_name(act))       # fp32 rows, or halves that are not 16-byte multiples
         return F.gated_act(y, _act_name(act))
@@ -257,9 +262,11 @@ class DSMultiGemmMoE(DSMoEBase):
         return M.row_gate_add_(out, F.linear(h, w_down)[:, : out.shape[1]].contiguous(), gate_logit)
 
     def forward(self, hidden_states, gate_w, mlp_1_w, mlp_2_w, mlp_1_b=None, mlp_2_b=None, gate_b=None,
-                shared=None) -> torch.Tensor:
+                shared=None, correction=None) -> torch.Tensor:
         """``gate_w`` ``[E (+ 1), H]``: the experts' router rows and, with ``shared_features``, one more row whose logit
-        gates the shared expert ``shared = (w_up [Fs, H], w_down [H, Fs])``; ``gate_b`` the logits' bias."""
+        gates the shared expert ``shared = (w_up [Fs, H], w_down [H, Fs])``; ``gate_b`` the logits' bias.  With
+        ``identity_experts`` the router has ``E + identity_experts`` rows (the identity experts last) and
+        ``correction`` (fp32, one per router row) is added to the scores for the choice only."""
         c = self._config
         if c.router_dtype is not None and _dt(c.router_dtype) == DtypeEnum.fp32 and gate_w.dtype == torch.float32:
             logits = M.router_logits(hidden_states, gate_w, gate_b)       # 32-bit product straight from the 16-bit rows
@@ -272,22 +279,31 @@ class DSMultiGemmMoE(DSMoEBase):
         if c.shared_features > 0:
             shared_logit = logits[:, c.n_experts].float()
             logits = logits[:, : c.n_experts].contiguous()
-        out = self._routed(hidden_states, logits, mlp_1_w, mlp_2_w, mlp_1_b, mlp_2_b)
+        out = self._routed(hidden_states, logits, mlp_1_w, mlp_2_w, mlp_1_b, mlp_2_b, correction)
         if shared_logit is not None:
             out = self._shared(out, hidden_states, shared_logit, shared)
         self._output = out
         return out
 
-    def _routed(self, hidden_states, logits, mlp_1_w, mlp_2_w, mlp_1_b, mlp_2_b) -> torch.Tensor:
+    def _routed(self, hidden_states, logits, mlp_1_w, mlp_2_w, mlp_1_b, mlp_2_b, correction=None) -> torch.Tensor:
         c = self._config
-        scores, assign, offsets, counts = moe_ops.top_k_gating(logits, c.top_k, renormalize=c.normalize_scores,
-                                                               score_function=c.score_function)
+        n_id = c.identity_experts
+        if logits.shape[1] != c.n_experts + n_id:
+            raise ValueError(f"the router has {logits.shape[1]} outputs for {c.n_experts} experts and {n_id} identity experts")
+        if c.score_correction or c.n_groups > 1 or c.score_scale != 1.0 or n_id > 0:
+            scores, assign, offsets, counts = moe_ops.top_k_gating(
+                logits, c.top_k, score_function=c.score_function, correction=correction if c.score_correction else None,
+                n_groups=c.n_groups, keep_groups=c.keep_groups, scale=c.score_scale)
+        else:
+            scores, assign, offsets, counts = moe_ops.top_k_gating(logits, c.top_k, renormalize=c.normalize_scores,
+                                                                   score_function=c.score_function)
         from .....moe import fused_ep
         if fused_ep.grouped_inference_ok(hidden_states, mlp_1_w, mlp_2_w, mlp_1_b, mlp_2_b):
             # one grouped tcgen05 GEMM per projection over expert-contiguous rows, no host synchronisation
             self._output = fused_ep.grouped_experts_inference(
                 hidden_states, scores, assign, offsets, counts, mlp_1_w, mlp_2_w,
-                lambda t: _apply_activation(t, None, c.activation), c.top_k, weight_input=c.weight_input)
+                lambda t: _apply_activation(t, None, c.activation, c.activation_limit), c.top_k,
+                weight_input=c.weight_input, n_identity=n_id)
             return self._output
         if c.weight_input:
             moe_in, cumsum, slots = moe_ops.moe_scatter_scaled(hidden_states, scores, assign, offsets, counts)
@@ -297,9 +313,11 @@ class DSMultiGemmMoE(DSMoEBase):
         out = torch.empty_like(moe_in)
         lo = 0
         for e, hi in enumerate(cumsum.tolist()):
-            if hi > lo:
+            if hi > lo and e >= c.n_experts:          # an identity expert hands its rows on
+                out[lo:hi] = moe_in[lo:hi]
+            elif hi > lo:
                 h = _apply_activation(F.linear(moe_in[lo:hi], mlp_1_w[e]),
-                                      None if mlp_1_b is None else mlp_1_b[e], c.activation)
+                                      None if mlp_1_b is None else mlp_1_b[e], c.activation, c.activation_limit)
                 y = F.linear(h, mlp_2_w[e])
                 out[lo:hi] = y if mlp_2_b is None else y + mlp_2_b[e]
             lo = hi
@@ -484,9 +502,12 @@ class DSSandwichRMSNorm(DSPreNormBase):
     def supports_config(config: DSNormConfig) -> bool:
         return NormTypeEnum(config.type) == NormTypeEnum.RMSNorm and _dt(config.residual_dtype) == DtypeEnum.fp32
 
-    def forward(self, residual, hidden_states, gamma, beta=None, gamma_post=None, extra=None, mult=1.0, copy_out=False):
+    def forward(self, residual, hidden_states, gamma, beta=None, gamma_post=None, extra=None, mult=1.0, copy_out=False,
+                channel_scale=None, gamma_offset=0.0):
+        """``channel_scale`` ``[W]``: what the closed sublayer adds is also multiplied per channel (a layer scale);
+        ``gamma_offset``: the opening norm's weight is ``gamma_offset + gamma`` (1 for weights stored around zero)."""
         y = M.resid_norm_step(residual, hidden_states, gamma_post, extra, gamma, self._config.eps,
-                              _dt(self._config.output_dtype).torch, mult, copy_out)
+                              _dt(self._config.output_dtype).torch, mult, copy_out, channel_scale, gamma_offset)
         return residual, y
 
 
@@ -550,6 +571,51 @@ class DSGatedDeltaMixer(_RecurrentMixer):
                                 n, dv, True)
         return M.group_norm_gate(o, projected[:, C: C + H * dv], weights.norm, dv, c.eps, False,
                                  _dt(c.output_dtype).torch)
+
+
+@DSRecurrentMixerRegistry.register_module
+class DSChannelDeltaMixer(_RecurrentMixer):
+    """Gated delta rule whose decay differs per key channel.  Projection columns: ``q (G n) | k (G n) | v (H dv) | b (H) |
+    a (ra) | g (rg)``; q, k, v pass a short convolution + SiLU, q and k become unit vectors (q also times ``n^-1/2``),
+    ``beta = sigmoid(b)``.  The decay comes from a two-step projection: ``decay[h, c] = exp(-exp(A_log[h]) softplus(
+    (w_a2 a)[h n + c] + dt_bias[h n + c]))``, one factor per head and key channel that multiplies the rows of the matrix
+    memory belonging to that channel; then ``u = beta (v - S^T k); S <- S + k u^T; o = S^T q``.  The output is ``o /
+    rms(o) * norm * sigmoid(w_g2 g)`` per head.  ``weights``: ``conv_w`` ``[2 G n + H dv, taps]``, ``A_log`` fp32 ``[H]``,
+    ``dt_bias`` fp32 ``[H n]``, ``w_a2`` ``[H n, ra]``, ``w_g2`` ``[H dv, rg]``, ``norm`` ``[dv]``."""
+
+    @staticmethod
+    def name() -> str:
+        return "channel_delta_mixer"
+
+    @staticmethod
+    def supports_config(config: DSRecurrentMixerConfig) -> bool:
+        return (config.kind == "channel_delta" and config.key_dim <= 256 and 1 <= config.conv_taps <= 16
+                and config.n_heads % config.n_heads_kv == 0)
+
+    @property
+    def conv_channels(self) -> int:
+        c = self._config
+        return 2 * c.n_heads_kv * c.key_dim + c.n_heads * c.value_dim
+
+    def forward(self, projected, weights, states, batch):
+        c = self._config
+        H, G, n, dv = c.n_heads, c.n_heads_kv, c.key_dim, c.value_dim
+        C = self.conv_channels
+        conv_state, S = states
+        info, t2s = batch.seq_info(), batch.token_to_seq()
+        xin = projected[:, :C]
+        x = M.conv_silu(xin, weights.conv_w, None, conv_state, info, t2s)
+        M.conv_state_update(xin, conv_state, info)
+        M.unit_norm_heads(x, 0, G, n, n ** -0.5, c.unit_norm_eps)
+        M.unit_norm_heads(x, G * n, G, n, 1.0, c.unit_norm_eps)
+        ra, rg = weights.w_a2.shape[1], weights.w_g2.shape[1]
+        a0 = C + H
+        a_raw = F.linear(projected[:, a0: a0 + ra], weights.w_a2)[:, : H * n]
+        gate = F.linear(projected[:, a0 + ra: a0 + ra + rg], weights.w_g2)[:, : H * dv]
+        decay, beta = M.channel_decay_gates(a_raw, projected[:, C: C + H], weights.A_log, weights.dt_bias, H, n)
+        o = M.linear_recurrence(x[:, G * n: 2 * G * n], x[:, : G * n], x[:, 2 * G * n:], decay, beta, None, S, info, H, G,
+                                n, dv, True)
+        return M.group_norm_gate(o, gate, weights.norm, dv, c.eps, False, _dt(c.output_dtype).torch, sigmoid=True)
 
 
 @DSRecurrentMixerRegistry.register_module
@@ -651,11 +717,16 @@ class DSLatentSinkAttention(DSSelfAttentionBase):
     their own.  The up-projections never run over the cache: a query head's unrotated part is carried through the key
     up-projection (``q_abs = W_uk[h]^T q``), attention runs in the latent space with ``[q_abs | q_rot]`` against
     ``[latent | k_rot]`` and the latent itself as value, and the value up-projection is applied to the attended latent.
-    Causal or sliding-window mask, optional sink logit; scores, weights and the weighted sum are fp32.
+    Causal or sliding-window mask, optional sink logit; scores, weights and the weighted sum are fp32.  With
+    ``q_direct`` the queries are columns of the fused projection itself (no query latent).  ``rotary_scaling`` slows
+    the long-wavelength pairs of the rotation (see :class:`RotaryScalingConfig`) and scales cos and sin.  With
+    ``output_gate`` the heads' outputs are multiplied by the sigmoid of further columns of the fused projection: one
+    per output channel, or one per head (``output_gate_per_head``).
 
     ``forward(projected, cache, batch, inv_freqs, weights)``: ``projected`` ``[T, q_rank + kv_latent_dim +
-    rope_head_dim (+ padding)]`` is the fused down-projection; ``weights`` has ``q_norm``, ``w_uq`` ``[H (d + rot),
-    q_rank]``, ``kv_norm``, ``w_uk`` ``[H, d, r]``, ``w_uv_t`` ``[H, r, dv]`` and ``sink``.  Returns ``[T, H dv]``."""
+    rope_head_dim (+ gate columns) (+ padding)]`` is the fused down-projection (``q_direct``: ``H (d + rot)`` query
+    columns in place of the ``q_rank`` latent ones); ``weights`` has ``q_norm``, ``w_uq`` ``[H (d + rot), q_rank]`` (not
+    with ``q_direct``), ``kv_norm``, ``w_uk`` ``[H, d, r]``, ``w_uv_t`` ``[H, r, dv]`` and ``sink``.  Returns ``[T, H dv]``."""
 
     @staticmethod
     def name() -> str:
@@ -681,8 +752,27 @@ class DSLatentSinkAttention(DSSelfAttentionBase):
         if n_rot % 2 or n_rot > config.rope_head_dim:
             raise ValueError(f"cannot rotate {n_rot} of {config.rope_head_dim} channels in pairs")
         base = 10000.0 if rot is None else rot.theta_base
-        self._inv_freq = torch.pow(torch.tensor(float(base), dtype=torch.float32),
-                                   -torch.arange(0, n_rot, 2, dtype=torch.float32) / max(n_rot, 1))
+        self._inv_freq, self._rot_amp = self.rotary_table(n_rot, base, config.rotary_scaling)
+
+    @staticmethod
+    def rotary_table(n_rot: int, base: float, scaling=None):
+        """fp32 angular frequencies ``base^(-2i / n_rot)`` of the ``n_rot / 2`` pairs and the factor on cos and sin.  With
+        ``scaling``: let ``pair(t) = n_rot ln(original / (2 pi t)) / (2 ln base)`` be the (fractional) pair that makes
+        ``t`` turns over the original context, ``lo = max(floor(pair(fast)), 0)``, ``hi = min(ceil(pair(slow)), n_rot - 1)``
+        and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``; pair ``i`` turns at ``f_i / factor * ramp_i + f_i *
+        (1 - ramp_i)`` and the amplitude is ``0.1 ln(factor) + 1``.  Evaluated in float64, stored as float32."""
+        i = torch.arange(0, n_rot, 2, dtype=torch.float64) / 2.0
+        f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / max(n_rot, 1))
+        amp = 1.0
+        if scaling is not None and n_rot > 0:
+            def pair(turns: float) -> float:
+                return n_rot * math.log(scaling.original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+            lo = max(math.floor(pair(scaling.fast)), 0)
+            hi = min(math.ceil(pair(scaling.slow)), n_rot - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            f = f / scaling.factor * ramp + f * (1.0 - ramp)
+            amp = 0.1 * math.log(scaling.factor) + 1.0
+        return f.to(torch.float32), float(amp)
 
     @property
     def kv_block_size(self) -> int:
@@ -703,16 +793,21 @@ class DSLatentSinkAttention(DSSelfAttentionBase):
         H, d, rot, r, dv = c.n_heads_q, c.head_size, c.rope_head_dim, c.kv_latent_dim, c.v_head_size or c.head_size
         cache = kv_cache[0] if isinstance(kv_cache, (tuple, list)) else kv_cache
         T = projected.shape[0]
-        q_rank = weights.w_uq.shape[1]
         if self._inv_freq.device != projected.device:
             self._inv_freq = self._inv_freq.to(projected.device)
         t2s, pos, tables = batch.token_to_seq(), batch.token_positions(), batch.block_tables()
-        cq = M.rms_norm_slice(projected[:, :q_rank], weights.q_norm, c.qk_norm_eps)
-        q = F.linear(cq, weights.w_uq)                                         # [T, H (d + rot)]
-        q_nope = q.view(T, H, d + rot)[:, :, :d].transpose(0, 1)              # [H, T, d]
+        if c.q_direct:
+            q_rank = H * (d + rot)
+            q = projected[:, :q_rank]                                          # [T, H (d + rot)], a column slice
+            q_nope = q.unflatten(1, (H, d + rot))[:, :, :d].transpose(0, 1)    # [H, T, d], strided
+        else:
+            q_rank = weights.w_uq.shape[1]
+            cq = M.rms_norm_slice(projected[:, :q_rank], weights.q_norm, c.qk_norm_eps)
+            q = F.linear(cq, weights.w_uq)[:, : H * (d + rot)]                 # [T, H (d + rot)]
+            q_nope = q.unflatten(1, (H, d + rot))[:, :, :d].transpose(0, 1)    # [H, T, d]
         q_abs = torch.bmm(q_nope, weights.w_uk).transpose(0, 1)               # [T, H, r], strided
         qf = M.latent_qk_prepare(q, q_abs, projected[:, q_rank: q_rank + r + rot], weights.kv_norm, self._inv_freq, cache,
-                                 t2s, pos, tables, H, d, rot, c.qk_norm_eps)
+                                 t2s, pos, tables, H, d, rot, c.qk_norm_eps, self._rot_amp)
         window = int(c.masking_args["size"]) if MaskingType(c.masking_type) == MaskingType.sliding_window else 0
         out_dt = _dt(c.output_dtype).torch
         atoms, n_long = None, 0
@@ -731,7 +826,14 @@ class DSLatentSinkAttention(DSSelfAttentionBase):
                                               window=window, value_cols=n, value_col0=c0).view(T, H, n))
             lat = torch.cat(parts, dim=2)
         ctx = torch.bmm(lat.view(T, H, r).transpose(0, 1), weights.w_uv_t)     # [H, T, dv]
-        return ctx.transpose(0, 1).reshape(T, H * dv)
+        ctx = ctx.transpose(0, 1).reshape(T, H * dv)
+        if c.output_gate:
+            g0 = q_rank + r + rot
+            if c.output_gate_per_head:
+                M.sigmoid_gate_rows_(ctx, projected[:, g0: g0 + H], dv)
+            else:
+                M.sigmoid_gate_rows_(ctx, projected[:, g0: g0 + H * dv], 1)
+        return ctx
 
 
 @DSPostNormRegistry.register_module

@@ -238,23 +238,28 @@ def make_plan(ep: FusedEP, counts, assign, offsets) -> EPPlan:
 
 @torch.no_grad()
 def grouped_experts_inference(x, scores, assign, offsets, counts, w1, w2, activation, top_k: int,
-                              weight_input: bool = False):
+                              weight_input: bool = False, n_identity: int = 0):
     """Inference MoE body without a host synchronisation: expert-contiguous rows through the plan / push kernels (one
     rank: every "peer" access is local), ONE grouped GEMM per projection over the 256-aligned groups, weighted
     un-permute through the pull kernel.  ``w1`` ``[E, N1, H]``, ``w2`` ``[E, H, F]`` (stacked expert weights),
     ``activation``: callable on the first projection's output (e.g. SwiGLU).  ``weight_input``: the routing weight
     scales the rows on their way INTO the experts (the push kernel multiplies) and the outputs are summed unweighted.
+    ``n_identity``: the assignments run over ``E + n_identity`` experts of which the last ``n_identity`` have no weights
+    and return their input: their row groups skip both products and are copied from the receive to the return buffer.
     Replaces the per-expert loop over
     ``cumsum.tolist()`` (reference: ``inference/v2/kernels/cutlass_ops/moe_gemm``)."""
     from ..ops.gemm_ext import grouped_gemm_nt
     T, H = x.shape
     E = w1.shape[0]
-    ep = FusedEP.get(None, H, E, T, top_k, 1.0)
+    ep = FusedEP.get(None, H, E + n_identity, T, top_k, 1.0)
     plan = make_plan(ep, counts, assign, offsets)
     wts = scores.to(torch.float32).contiguous()
     ep.push(x.contiguous(), plan, weights=wts if weight_input else None)
     h = activation(grouped_gemm_nt(ep.recv_rows, w1, plan.group_offsets))
     grouped_gemm_nt(h, w2, plan.group_offsets, out=ep.ret_rows)
+    if n_identity > 0:
+        from ..ops.moe_ops import copy_group_rows_
+        copy_group_rows_(ep.ret_rows, ep.recv_rows, plan.group_offsets, E, E + n_identity)
     y = torch.empty((T, H), dtype=x.dtype, device=x.device)
     ep.pull(y, plan, weights=None if weight_input else wts)
     return y

@@ -17,6 +17,8 @@ from ..native import lib as _lib
 
 _lib.register({
     "sxb_top_k_gating": "ppppp" "iiii" "i" "p",
+    "sxb_grouped_top_k_gating": "pppppp" "iiiii" "f" "p",
+    "sxb_copy_group_rows": "ppp" "iii" "l" "p",
     "sxb_moe_scatter": "ppppppp" "iiiii" "p",
     "sxb_moe_scatter_scaled": "pppppppp" "iiiii" "p",
     "sxb_moe_gather": "pppp" "iii" "p",
@@ -24,11 +26,17 @@ _lib.register({
 })
 
 
-def top_k_gating(logits: torch.Tensor, top_k: int, renormalize: bool = True, score_function: str = "softmax"):
+def top_k_gating(logits: torch.Tensor, top_k: int, renormalize: bool = True, score_function: str = "softmax",
+                 correction: torch.Tensor = None, n_groups: int = 1, keep_groups: int = 1, scale: float = 1.0):
     """``logits`` [T, E] -> ``(scores fp32 [T,K], assignments int32 [T,K], offsets int32 [T,K], counts int32 [E])``.
 
     ``score_function`` ``"softmax"``: scores are the softmax over all experts; ``"sigmoid"``: every expert is scored on
     its own with ``sigmoid(logit)``.  The ``top_k`` largest win either way; ``renormalize`` divides them by their sum.
+
+    Group-limited choice (softmax scores only; taken when ``correction`` is given, ``n_groups > 1`` or ``scale != 1``):
+    the winners are the ``top_k`` largest ``score + correction`` (``correction`` fp32 ``[E]``) among the experts of the
+    ``keep_groups`` groups -- of ``n_groups`` equal groups of neighbouring experts -- whose best ``score + correction``
+    is largest; the returned scores are the winners' plain scores divided by their sum (+ 1e-20), times ``scale``.
 
     ``offsets[t,k]`` is the arrival index of token ``t`` inside expert ``assignments[t,k]`` (a permutation of
     ``range(counts[e])`` per expert; on CUDA the order is nondeterministic, on CPU it is token order)."""
@@ -40,6 +48,39 @@ def top_k_gating(logits: torch.Tensor, top_k: int, renormalize: bool = True, sco
     assign = torch.empty(T, top_k, dtype=torch.int32, device=dev)
     offsets = torch.empty(T, top_k, dtype=torch.int32, device=dev)
     counts = torch.empty(E, dtype=torch.int32, device=dev)
+    grouped = correction is not None or n_groups > 1 or scale != 1.0
+    if grouped:
+        if score_function != "softmax":
+            raise ValueError("the group-limited choice scores with the softmax over all experts")
+        if E % n_groups or not 1 <= keep_groups <= n_groups or top_k > keep_groups * (E // n_groups):
+            raise ValueError(f"cannot choose {top_k} of {E} experts in {keep_groups} of {n_groups} groups")
+    if grouped and logits.is_cuda:
+        logits = logits.float().contiguous()
+        corr = None if correction is None else correction.float().contiguous()
+        _lib.call("sxb_grouped_top_k_gating", logits.data_ptr(), _lib.ptr(corr), scores.data_ptr(), assign.data_ptr(),
+                  offsets.data_ptr(), counts.data_ptr(), T, E, top_k, int(n_groups), int(keep_groups), float(scale),
+                  _lib.stream_ptr())
+        return scores, assign, offsets, counts
+    if grouped:
+        probs = torch.softmax(logits.float(), dim=-1)
+        choice = probs if correction is None else probs + correction.float()
+        if keep_groups < n_groups:
+            per = E // n_groups
+            best = choice.view(T, n_groups, per).max(dim=-1).values
+            kept = torch.zeros(T, n_groups, dtype=torch.bool, device=dev)
+            kept.scatter_(1, torch.topk(best, keep_groups, dim=-1).indices, True)
+            choice = choice.masked_fill(~kept.repeat_interleave(per, dim=1), float("-inf"))
+        a = torch.topk(choice, top_k, dim=-1).indices
+        s = probs.gather(1, a)
+        s = s / (s.sum(dim=-1, keepdim=True) + 1e-20) * scale
+        flat = a.reshape(-1)
+        onehot = torch.nn.functional.one_hot(flat, E)
+        order = (torch.cumsum(onehot, dim=0) - 1).gather(1, flat[:, None]).squeeze(1)
+        scores.copy_(s)
+        assign.copy_(a.to(torch.int32))
+        offsets.copy_(order.view(T, top_k).to(torch.int32))
+        counts.copy_(onehot.sum(0).to(torch.int32))
+        return scores, assign, offsets, counts
     if logits.is_cuda:
         logits = logits.contiguous()
         _lib.call("sxb_top_k_gating", logits.data_ptr(), scores.data_ptr(), assign.data_ptr(), offsets.data_ptr(),
@@ -171,3 +212,20 @@ def moe_scatter_scaled(x: torch.Tensor, scores: torch.Tensor, assign: torch.Tens
     scaled = (x.float()[:, None, :] * scores[:, :, None]).to(x.dtype).reshape(T * K, H)
     moe_in[slots.long().reshape(-1)] = scaled
     return moe_in, cumsum, slots
+
+
+def copy_group_rows_(dst: torch.Tensor, src: torch.Tensor, offsets: torch.Tensor, g_lo: int, g_hi: int) -> torch.Tensor:
+    """``dst[offsets[g_lo] : offsets[g_hi]] = src[the same rows]`` for expert-sorted row buffers whose group offsets
+    (int32, ``[groups + 1]``) live on the device: experts that hand their input on unchanged, without a host read."""
+    if g_hi <= g_lo:
+        return dst
+    if src.is_cuda:
+        if offsets.dtype != torch.int32 or not src.is_contiguous() or not dst.is_contiguous() or src.dtype != dst.dtype \
+                or src.shape[1] != dst.shape[1]:
+            raise ValueError("expected contiguous row buffers of one shape and dtype and int32 offsets")
+        _lib.call("sxb_copy_group_rows", src.data_ptr(), dst.data_ptr(), offsets.data_ptr(), int(g_lo), int(g_hi),
+                  src.shape[1] * src.element_size(), min(src.shape[0], dst.shape[0]), _lib.stream_ptr())
+        return dst
+    lo, hi = int(offsets[g_lo]), int(offsets[g_hi])
+    dst[lo:hi] = src[lo:hi]
+    return dst

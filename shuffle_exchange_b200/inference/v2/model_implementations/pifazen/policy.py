@@ -135,8 +135,8 @@ class PifazenPolicy(InferenceV2Policy):
                 H, n, dv = L.n_heads, L.key_dim, L.value_dim
                 # the two-step projections' first steps ride in the fused projection, their widths padded to whole
                 # 16-byte rows (zero rows here, zero columns in the second step)
-                lw["w_in"] = pad_rows(torch.cat([cat([m + "q", m + "k", m + "v", m + "b"]), pad_rows(get(m + "a1")),
-                                                 pad_rows(get(m + "g1"))], dim=0))
+                lw["w_in"] = pad_rows(torch.cat([cat([m + "q", m + "k", m + "v"]), pad_rows(get(m + "b")),
+                                                 pad_rows(get(m + "a1")), pad_rows(get(m + "g1"))], dim=0))
                 lw["conv_w"] = cat([m + "q.conv", m + "k.conv", m + "v.conv"])
                 if lw["conv_w"].shape[1] != L.conv_taps:
                     raise ValueError(f"{m}*.conv have {lw['conv_w'].shape[1]} taps, the configuration says {L.conv_taps}")

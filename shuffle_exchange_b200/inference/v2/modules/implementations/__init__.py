@@ -575,8 +575,8 @@ class DSGatedDeltaMixer(_RecurrentMixer):
 
 @DSRecurrentMixerRegistry.register_module
 class DSChannelDeltaMixer(_RecurrentMixer):
-    """Gated delta rule whose decay differs per key channel.  Projection columns: ``q (G n) | k (G n) | v (H dv) | b (H) |
-    a (ra) | g (rg)``; q, k, v pass a short convolution + SiLU, q and k become unit vectors (q also times ``n^-1/2``),
+    """Gated delta rule whose decay differs per key channel.  Projection columns: ``q (G n) | k (G n) | v (H dv) | b (H,
+    padded to a multiple of 8) | a (ra) | g (rg)``; q, k, v pass a short convolution + SiLU, q and k become unit vectors (q also times ``n^-1/2``),
     ``beta = sigmoid(b)``.  The decay comes from a two-step projection: ``decay[h, c] = exp(-exp(A_log[h]) softplus(
     (w_a2 a)[h n + c] + dt_bias[h n + c]))``, one factor per head and key channel that multiplies the rows of the matrix
     memory belonging to that channel; then ``u = beta (v - S^T k); S <- S + k u^T; o = S^T q``.  The output is ``o /
@@ -609,7 +609,7 @@ class DSChannelDeltaMixer(_RecurrentMixer):
         M.unit_norm_heads(x, 0, G, n, n ** -0.5, c.unit_norm_eps)
         M.unit_norm_heads(x, G * n, G, n, 1.0, c.unit_norm_eps)
         ra, rg = weights.w_a2.shape[1], weights.w_g2.shape[1]
-        a0 = C + H
+        a0 = C + (H + 7) // 8 * 8
         a_raw = F.linear(projected[:, a0: a0 + ra], weights.w_a2)[:, : H * n]
         gate = F.linear(projected[:, a0 + ra: a0 + ra + rg], weights.w_g2)[:, : H * dv]
         decay, beta = M.channel_decay_gates(a_raw, projected[:, C: C + H], weights.A_log, weights.dt_bias, H, n)

@@ -241,6 +241,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
             and x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0:
         if not x.is_contiguous():
             x = x.contiguous()
+        if x.data_ptr() % 16:               # a one-row column slice counts as contiguous wherever it starts
+            x = x.clone()
         return _Linear.apply(x, weight, bias)
     if x.is_cuda:
         # fp16 / fp32 operands or rows that are not 16-byte multiples: the tcgen05 GEMM takes bf16 only, the library

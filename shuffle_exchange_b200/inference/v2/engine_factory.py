@@ -87,7 +87,7 @@ def build_engine_from_ds_checkpoint(path: str, engine_config: RaggedInferenceEng
 def build_hf_engine(path: str, engine_config: RaggedInferenceEngineConfig = None,
                     debug_level: int = logging.INFO, dtype: torch.dtype = None, device=None) -> InferenceEngineV2:
     """Engine for a local HuggingFace checkpoint directory (or a serialized v2 checkpoint) of a supported
-    architecture: llama, mistral, mixtral, falcon, opt, phi, phi3, qwen, qwen2, qwen2_moe, fomalix, kekopel, ridazen.  ``dtype`` overrides
+    architecture: llama, mistral, mixtral, falcon, opt, phi, phi3, qwen, qwen2, qwen2_moe, fomalix, kekopel, ridazen, pifazen.  ``dtype`` overrides
     the checkpoint's activation dtype (``torch.float32`` evaluates a model in full precision where it supports that)."""
     engine_config = engine_config or RaggedInferenceEngineConfig()
     if os.path.exists(os.path.join(path, "ds_model_config.pkl")):

@@ -240,7 +240,8 @@ class DSMultiGemmMoE(DSMoEBase):
     @staticmethod
     def supports_config(config: DSMoEConfig) -> bool:
         return (_dt(config.input_dtype) == _dt(config.output_dtype) and 1 <= config.top_k <= 8
-                and config.top_k <= config.n_experts and config.score_function in ("softmax", "sigmoid"))
+                and config.top_k <= config.n_experts + config.identity_experts
+                and config.score_function in ("softmax", "sigmoid"))
 
     def __init__(self, config, implementation_config):
         super().__init__(config, implementation_config)

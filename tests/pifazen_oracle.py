@@ -259,8 +259,9 @@ def forward(config: Dict, tensors: Dict[str, torch.Tensor], tokens: List[int], l
 
 
 # ------------------------------------------------------------------------------------------------ random checkpoints
-def random_weights(config: Dict, seed: int = 0, dtype=torch.bfloat16) -> Dict[str, torch.Tensor]:
-    """A checkpoint of the configuration's shapes; values are rounded to ``dtype`` so that both sides read the same."""
+def random_weights(config: Dict, seed: int = 0, dtype=torch.bfloat16, rank: int = 6) -> Dict[str, torch.Tensor]:
+    """A checkpoint of the configuration's shapes; values are rounded to ``dtype`` so that both sides read the same.
+    ``rank`` is the inner size of the delta rule's two-step projections (a tensor shape, not a configuration entry)."""
     gen = torch.Generator().manual_seed(seed)
     W = int(config["width"])
 
@@ -279,7 +280,6 @@ def random_weights(config: Dict, seed: int = 0, dtype=torch.bfloat16) -> Dict[st
         x = p + "mix."
         if kind == "channel_delta":
             H, G, n, dv, taps = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), int(m["conv"])
-            rank = int(m.get("_rank", 6))
             for name, rows in (("q", G * n), ("k", G * n), ("v", H * dv)):
                 t[x + name] = lin(rows, W, 2.0)
                 t[x + name + ".conv"] = rnd(rows, taps, std=0.6)

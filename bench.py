@@ -57,10 +57,11 @@ def parse():
                     help="instead of the training step: serving throughput (prefill and decode through the ragged "
                          "engine) of the hybrid Fomalix stack beside a Llama stack of equal size, for the comma-separated "
                          "sizes (w1024, w2048, w4096; 'all'), with device times of their kernels against the memory roofline")
-    ap.add_argument("--serve-model", default="fomalix", choices=["fomalix", "kekopel", "ridazen"],
+    ap.add_argument("--serve-model", default="fomalix", choices=["fomalix", "kekopel", "ridazen", "pifazen"],
                     help="with --serve: 'kekopel' measures the Kekopel stack beside the Fomalix stack of equal size (and "
                          "each of its kernels beside the like Fomalix kernel) instead of Fomalix beside Llama; 'ridazen' "
-                         "the Ridazen stack beside a Fomalix stack of attention layers of equal size")
+                         "the Ridazen stack beside a Fomalix stack of attention layers of equal size; 'pifazen' the "
+                         "Pifazen stack beside the Kekopel stack of equal size")
     ap.add_argument("--serve-prefill", type=int, default=4096)
     ap.add_argument("--serve-batch", type=int, default=64)
     ap.add_argument("--serve-context", type=int, default=2560)

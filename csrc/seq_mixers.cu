@@ -1185,6 +1185,36 @@ gated_act_rows_kernel(const T* __restrict__ in, T* __restrict__ out, long long t
 }
 
 
+__device__ __forceinline__ float gated_act_value(float gte, float up, int act, float limit) {
+  if (act == 5) {
+    gte = fminf(gte, limit);
+    return gte * sigmoid_f(1.702f * gte) * (fminf(fmaxf(up, -limit), limit) + 1.f);
+  }
+  float a = gte;
+  if (act == 2) a = 0.5f * gte * (1.f + tanhf(0.7978845608028654f * (gte + 0.044715f * gte * gte * gte)));
+  else if (act == 3) a = silu_f(gte);
+  else if (act == 1) a = fmaxf(gte, 0.f);
+  return a * up;
+}
+
+// The same with VEC consecutive channels per thread (16-byte accesses): F a multiple of VEC, rows 16-byte aligned.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+gated_act_rows_vec_kernel(const T* __restrict__ in, T* __restrict__ out, long long nvec, int fvec, int act, float limit) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nvec) return;
+  const long long r = i / fvec;
+  const int c = (int)(i % fvec) * VEC;
+  const int F = fvec * VEC;
+  struct alignas(16) Pack { T v[VEC]; };
+  const Pack g = *reinterpret_cast<const Pack*>(in + r * 2 * F + c);
+  const Pack u = *reinterpret_cast<const Pack*>(in + r * 2 * F + F + c);
+  Pack o;
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) o.v[j] = from_f32<T>(gated_act_value(to_f32<T>(g.v[j]), to_f32<T>(u.v[j]), act, limit));
+  *reinterpret_cast<Pack*>(out + r * F + c) = o;
+}
+
 // ------------------------------------------------------------------------------------------------ post-norm layers
 // Layers of the form  x <- x + scale (.) (sublayer(x + conv(x)) / rms * gain):  the sublayer reads the fp32 stream
 // through a short causal filter with a skip path, its output is normalised with ONE gain for all channels and scaled
@@ -1914,6 +1944,19 @@ SXB_API int sxb_gated_act_rows(const void* in, void* out, long long rows, int F,
                                void* stream) {
   const long long total = rows * F;
   if (total <= 0) return SXB_OK;
+  const int per = dtype == 0 ? 4 : 8;
+  if (F % per == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+      (dtype == 0 || dtype == 2)) {
+    const long long nv = total / per;
+    if (dtype == 0)
+      gated_act_rows_vec_kernel<float, 4><<<(unsigned)((nv + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+          (const float*)in, (float*)out, nv, F / 4, act, limit);
+    else
+      gated_act_rows_vec_kernel<__nv_bfloat16, 8><<<(unsigned)((nv + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+          (const __nv_bfloat16*)in, (__nv_bfloat16*)out, nv, F / 8, act, limit);
+    SXB_CHECK_LAUNCH();
+    return SXB_OK;
+  }
   SEQMIX_DISPATCH(dtype, (gated_act_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
                              (const T*)in, (T*)out, total, F, act, limit)));
   SXB_CHECK_LAUNCH();
@@ -2182,6 +2225,86 @@ power_norm_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, const
   }
 }
 
+// The same with the row held in registers between the two passes: VEC channels per 16-byte access, up to CH accesses per
+// thread (F <= 256 * VEC * CH), the three sums reduced together.
+template <typename T, int VEC, int CH>
+__global__ void __launch_bounds__(256)
+power_norm_act_vec_kernel(const T* __restrict__ x, const T* __restrict__ bias, const float* __restrict__ coef,
+                          T* __restrict__ out, int F, float eps) {
+  __shared__ float red[3][8];
+  struct alignas(16) Pack { T v[VEC]; };
+  const long long base = (long long)blockIdx.x * F;
+  const int nvec = F / VEC;
+  Pack z[CH];
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int k = 0; k < CH; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < nvec) {
+      z[k] = *reinterpret_cast<const Pack*>(x + base + (long long)i * VEC);
+      if (bias != nullptr) {
+        const Pack b = *reinterpret_cast<const Pack*>(bias + (long long)i * VEC);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) z[k].v[j] = from_f32<T>(to_f32<T>(z[k].v[j]) + to_f32<T>(b.v[j]));
+      }
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float v = to_f32<T>(z[k].v[j]), v2 = v * v;
+        s1 += v2, s2 += v2 * v2, s3 += v2 * v2 * v2;
+      }
+    }
+  }
+  s1 = warp_sum(s1), s2 = warp_sum(s2), s3 = warp_sum(s3);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[0][w] = s1, red[1][w] = s2, red[2][w] = s3;
+  __syncthreads();
+  s1 = s2 = s3 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s1 += red[0][i], s2 += red[1][i], s3 += red[2][i];
+  const float a = coef[0] / sqrtf(s1 / (float)F + eps), b = coef[1] / sqrtf(s2 / (float)F + eps),
+              c3 = coef[2] / sqrtf(s3 / (float)F + eps), e = coef[3];
+#pragma unroll
+  for (int k = 0; k < CH; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < nvec) {
+      Pack o;
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float v = to_f32<T>(z[k].v[j]);
+        o.v[j] = from_f32<T>(((c3 * v + b) * v + a) * v + e);
+      }
+      *reinterpret_cast<Pack*>(out + base + (long long)i * VEC) = o;
+    }
+  }
+}
+
+// channel_decay_gates with four consecutive key channels (one head: n is a multiple of 4) per thread.
+template <typename T>
+__global__ void __launch_bounds__(256)
+channel_decay_gates_vec_kernel(const T* __restrict__ a_raw, long long lda, const T* __restrict__ b_raw, long long ldb,
+                               const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                               float* __restrict__ decay, float* __restrict__ beta, int H, int n, long long total4) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total4) return;
+  const int Hn4 = H * n / 4;
+  const long long t = i / Hn4;
+  const int c = (int)(i % Hn4) * 4, h = c / n;
+  struct alignas(sizeof(T) * 4) Pack { T v[4]; };
+  const Pack a = *reinterpret_cast<const Pack*>(a_raw + t * lda + c);
+  const float4 db = *reinterpret_cast<const float4*>(dt_bias + c);
+  const float rate = -expf(A_log[h]);
+  float4 o;
+  o.x = expf(rate * softplus_f(to_f32<T>(a.v[0]) + db.x));
+  o.y = expf(rate * softplus_f(to_f32<T>(a.v[1]) + db.y));
+  o.z = expf(rate * softplus_f(to_f32<T>(a.v[2]) + db.z));
+  o.w = expf(rate * softplus_f(to_f32<T>(a.v[3]) + db.w));
+  *reinterpret_cast<float4*>(decay + t * (long long)H * n + c) = o;
+  if (c < H) {
+    const int hi = min(c + 4, H);
+    for (int j = c; j < hi; ++j) beta[t * H + j] = sigmoid_f(to_f32<T>(b_raw[t * ldb + j]));
+  }
+}
+
 }  // namespace seqmix
 }  // namespace sxb
 
@@ -2193,6 +2316,17 @@ SXB_API int sxb_channel_decay_gates(const void* a_raw, long long lda, const void
                                     void* stream) {
   const long long total = (long long)n_tokens * H * n;
   if (total <= 0) return SXB_OK;
+  const int esz = dtype == 0 ? 4 : 2;
+  if (n % 4 == 0 && lda % 4 == 0 && (reinterpret_cast<uintptr_t>(a_raw) % (4 * esz)) == 0 &&
+      ((reinterpret_cast<uintptr_t>(dt_bias) | reinterpret_cast<uintptr_t>(decay)) & 15) == 0) {
+    const long long total4 = total / 4;
+    SEQMIX_DISPATCH(dtype, (channel_decay_gates_vec_kernel<T><<<(unsigned)((total4 + 255) / 256), 256, 0,
+                                                               (cudaStream_t)stream>>>(
+                               (const T*)a_raw, lda, (const T*)b_raw, ldb, (const float*)A_log, (const float*)dt_bias,
+                               (float*)decay, (float*)beta, H, n, total4)));
+    SXB_CHECK_LAUNCH();
+    return SXB_OK;
+  }
   SEQMIX_DISPATCH(dtype, (channel_decay_gates_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
                              (const T*)a_raw, lda, (const T*)b_raw, ldb, (const float*)A_log, (const float*)dt_bias,
                              (float*)decay, (float*)beta, H, n, total)));
@@ -2235,6 +2369,29 @@ SXB_API int sxb_sigmoid_gate_rows(void* x, const void* gate, long long ldg, long
 SXB_API int sxb_power_norm_act(const void* in, const void* bias, const void* coef, void* out, long long rows, int F,
                                float eps, int dtype, void* stream) {
   if (rows <= 0 || F <= 0) return SXB_OK;
+  const int per = dtype == 0 ? 4 : 8;
+  const bool aligned = F % per == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
+                                         reinterpret_cast<uintptr_t>(bias)) & 15) == 0;
+  if (aligned && F <= 256 * per * 8 && (dtype == 0 || dtype == 2)) {
+    cudaStream_t s = (cudaStream_t)stream;
+    const int chunks = (F / per + 255) / 256;
+#define POWER_NORM(CH)                                                                                              \
+  do {                                                                                                              \
+    if (dtype == 0)                                                                                                 \
+      power_norm_act_vec_kernel<float, 4, CH><<<(unsigned)rows, 256, 0, s>>>(                                       \
+          (const float*)in, (const float*)bias, (const float*)coef, (float*)out, F, eps);                           \
+    else                                                                                                            \
+      power_norm_act_vec_kernel<__nv_bfloat16, 8, CH><<<(unsigned)rows, 256, 0, s>>>(                               \
+          (const __nv_bfloat16*)in, (const __nv_bfloat16*)bias, (const float*)coef, (__nv_bfloat16*)out, F, eps);   \
+  } while (0)
+    if (chunks <= 1) POWER_NORM(1);
+    else if (chunks <= 2) POWER_NORM(2);
+    else if (chunks <= 4) POWER_NORM(4);
+    else POWER_NORM(8);
+#undef POWER_NORM
+    SXB_CHECK_LAUNCH();
+    return SXB_OK;
+  }
   SEQMIX_DISPATCH(dtype, (power_norm_act_kernel<T><<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
                              (const T*)in, (const T*)bias, (const float*)coef, (T*)out, F, eps)));
   SXB_CHECK_LAUNCH();

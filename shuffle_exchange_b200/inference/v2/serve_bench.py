@@ -5,7 +5,10 @@ counterparts against the memory roofline.  ``bench.py --serve`` prints the resul
 post-scaled layers, dense and expert feed-forwards) next to the Fomalix stack of equal size, and the kernel table sets
 every Kekopel kernel beside the Fomalix kernel that does the like job.  With ``--serve-model ridazen`` the pair is a
 Ridazen stack (attention with filtered projections, distance-bucket bias and output gate, squared-ReLU experts with a
-shared expert, per-layer token input) next to a Fomalix stack of attention layers only at equal size.
+shared expert, per-layer token input) next to a Fomalix stack of attention layers only at equal size.  With
+``--serve-model pifazen`` the pair is a Pifazen stack (latent attention with output gates and scaled rotation, a delta rule
+with a decay per key channel, three-power dense feed-forward, clamped experts chosen among groups with identity experts)
+next to the Kekopel stack of equal size whose window holds every key.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up forwards, a buffer larger than L2 is rewritten between timed
 forwards.  Prefill: one request of ``prefill`` tokens in one forward.  Decode: ``batch`` requests with ``context`` tokens
@@ -700,6 +703,243 @@ def ridazen_kernel_table(z: Dict, prefill: int, batch: int, context: int, timer,
     return rows
 
 
+# ------------------------------------------------------------------------------------------------ Pifazen beside Kekopel
+PIFAZEN = dict(taps=4, rank=64, experts=8, identity=2, groups=2, keep=1, top=2, scale=2.0, limit=7.0,
+               yarn=dict(factor=8.0, original=1024, fast=32.0, slow=1.0))
+
+
+def pifazen_config(z: Dict) -> Dict:
+    kinds = ["latent_attention", "channel_delta", "latent_attention_2"]
+    lat = {"dim": z["head"], "heads": z["heads"], "kv_rank": LATENT["kv_rank"], "q_rank": LATENT["q_rank"],
+           "rot": {"base": 10000.0, "dims": LATENT["rot"]}, "rot_dim": LATENT["rot"],
+           "scale": (z["head"] + LATENT["rot"]) ** -0.5, "vdim": z["head"]}
+    lat2 = {k: v for k, v in lat.items() if k != "q_rank"}
+    lat2["rot"] = {"base": 10000.0, "dims": LATENT["rot"], "scaling": dict(PIFAZEN["yarn"])}
+    mixers = {"latent_attention": lat, "latent_attention_2": lat2,
+              "channel_delta": {"conv": PIFAZEN["taps"], "dim": z["head"], "heads": z["heads"], "kv_heads": z["heads"],
+                                "vdim": z["head"]}}
+    mlps = [{"ff": z["ff"], "kind": "dense"},
+            {"expert": {"ff": z["ff"] // 4, "limit": PIFAZEN["limit"]}, "kind": "moe",
+             "router": {"experts": PIFAZEN["experts"], "identity": PIFAZEN["identity"], "top": PIFAZEN["top"],
+                        "groups": {"count": PIFAZEN["groups"], "keep": PIFAZEN["keep"]}, "scale": PIFAZEN["scale"]}}]
+    layers = [{"type": kinds[i % 3], "mixer": mixers[kinds[i % 3]], "mlp": mlps[i % 2]} for i in range(z["layers"])]
+    return {"architecture": "Pifazen", "layers": layers, "norm": {"eps": 1e-5}, "vocab": VOCAB, "width": z["width"]}
+
+
+def pifazen_weights(cfg: Dict, device) -> Dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(0)
+    W, bf = cfg["width"], torch.bfloat16
+
+    def mat(o, i):
+        return (torch.randn(o, i, generator=g, device=device) / math.sqrt(i)).to(bf)
+
+    def vec(n, lo=0.5, hi=1.5):
+        return (torch.rand(n, generator=g, device=device) * (hi - lo) + lo).to(bf)
+
+    out = {"embed": mat(cfg["vocab"], W), "final.norm": vec(W, -0.2, 0.2)}
+    for i, L in enumerate(cfg["layers"]):
+        m, p = L["mixer"], f"l{i}."
+        for n in ("1", "2"):
+            out[p + "norm" + n], out[p + "ls" + n] = vec(W, -0.2, 0.2), vec(W, 0.2, 0.8)
+        if L["type"] == "channel_delta":
+            H, G, d, dv, taps, rk = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"], PIFAZEN["rank"]
+            for n, o in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                out[p + "mix." + n], out[p + "mix." + n + ".conv"] = mat(o, W), vec(o * taps, -0.5, 0.5).view(o, taps)
+            out[p + "mix.b"], out[p + "mix.A_log"] = mat(H, W), vec(H, -3.0, -1.0)
+            out[p + "mix.a1"], out[p + "mix.a2"], out[p + "mix.dt_bias"] = mat(rk, W), mat(H * d, rk), vec(H * d, -1, 1)
+            out[p + "mix.g1"], out[p + "mix.g2"] = mat(rk, W), mat(H * dv, rk)
+            out[p + "mix.norm"], out[p + "mix.o"] = vec(dv), mat(W, H * dv)
+        else:
+            H, d, rot, dv, r = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            if L["type"] == "latent_attention":
+                qr = m["q_rank"]
+                out[p + "mix.dq"], out[p + "mix.dq.norm"], out[p + "mix.uq"] = mat(qr, W), vec(qr), mat(H * (d + rot), qr)
+                out[p + "mix.g"] = mat(H * dv, W)
+            else:
+                out[p + "mix.q"], out[p + "mix.g"] = mat(H * (d + rot), W), mat(H, W)
+            out[p + "mix.dkv"], out[p + "mix.dkv.norm"] = mat(r + rot, W), vec(r)
+            out[p + "mix.uk"], out[p + "mix.uv"], out[p + "mix.o"] = mat(H * d, r), mat(H * dv, r), mat(W, H * dv)
+        mlp = L["mlp"]
+        if mlp["kind"] == "dense":
+            out[p + "mlp.up"], out[p + "mlp.up.b"] = mat(mlp["ff"], W), vec(mlp["ff"], -0.1, 0.1)
+            out[p + "mlp.down"], out[p + "mlp.down.b"] = mat(W, mlp["ff"]), vec(W, -0.1, 0.1)
+            out[p + "mlp.act"] = torch.tensor([0.6, 0.3, 0.2, 0.05], device=device).to(bf)
+        else:
+            F_, E, n_id = mlp["expert"]["ff"], mlp["router"]["experts"], mlp["router"]["identity"]
+            out[p + "mlp.router"], out[p + "mlp.correction"] = mat(E + n_id, W), vec(E + n_id, -0.05, 0.05)
+            for e in range(E):
+                out[p + f"mlp.e{e}.gate"], out[p + f"mlp.e{e}.up"] = mat(F_, W), mat(F_, W)
+                out[p + f"mlp.e{e}.down"] = mat(W, F_)
+    return out
+
+
+def build_pifazen(z: Dict, max_tokens: int, max_seqs: int, pages: int):
+    cfg = pifazen_config(z)
+    return build_engine_from_state_dict(cfg, pifazen_weights(cfg, "cuda"), _engine_config(max_tokens, max_seqs, pages),
+                                        dtype=torch.bfloat16)
+
+
+def pifazen_kernel_table(z: Dict, prefill: int, batch: int, context: int, timer, hbm_gbs: float,
+                         peak_tflops: Dict[str, float]) -> List[Dict]:
+    """Every kernel the Pifazen stack adds or takes in a new form, beside the kernel of the Kekopel / Fomalix stacks that
+    does the like job (``like``), at prefill (one request) and decode (``batch`` requests) shapes: device time,
+    algorithmic bytes and FLOPs, fraction of the roofline (the larger of bytes / copy bandwidth and FLOPs / the peak of
+    the unit the products run on)."""
+    from ...moe import fused_ep
+    from ...ops import functional as F
+    from ...ops import moe_ops
+    from .kernels import mixer_ops as M
+    from .modules.configs import RotaryScalingConfig
+    from .modules.implementations import DSLatentSinkAttention
+    from .ragged.ragged_wrapper import RaggedBatchWrapper
+    dev, bf = "cuda", torch.bfloat16
+    W, H, d, ff = z["width"], z["heads"], z["head"], z["ff"]
+    r, rot, rk = LATENT["kv_rank"], LATENT["rot"], PIFAZEN["rank"]
+    rows: List[Dict] = []
+
+    def add(name, like, phase, fn, nbytes, flops=0.0, pipe=None):
+        ms = timer(fn, 5, 3)
+        ideal_ms = nbytes / hbm_gbs / 1e6
+        if pipe is not None:
+            ideal_ms = max(ideal_ms, flops / peak_tflops[pipe] / 1e9)
+        rows.append({"kernel": name, "like": like, "phase": phase, "ms": round(ms, 4),
+                     "GB_s": round(nbytes / ms / 1e6, 1), "GFLOP_s": round(flops / ms / 1e6, 1), "pipe": pipe or "memory",
+                     "of_roofline": round(ideal_ms / ms, 3)})
+
+    for phase, T, n_seq, seen in (("prefill", prefill, 1, 0), ("decode", batch, batch, context)):
+        per = T // n_seq
+        tot = seen + per
+        n_pages_seq = (tot + 63) // 64
+        t2s = torch.arange(n_seq, device=dev, dtype=torch.int32).repeat_interleave(per)
+        pos = (torch.arange(per, device=dev, dtype=torch.int32) + seen).repeat(n_seq)
+        tables = torch.arange(n_seq * n_pages_seq, device=dev, dtype=torch.int32).view(n_seq, n_pages_seq)
+        info = torch.tensor([[i * per, per, seen, i] for i in range(n_seq)], dtype=torch.int32, device=dev)
+        x32 = torch.randn(T, W, device=dev)
+        y = torch.randn(T, W, device=dev).to(bf)
+        wv = torch.ones(W, device=dev, dtype=bf)
+        # closing a sublayer with a channel scale and opening the next with weights stored around zero
+        add("resid_norm_step (channel scale, weight offset)", None, phase,
+            lambda: M.resid_norm_step(x32, y, None, None, wv, 1e-5, bf, 1.0, False, wv, 1.0), T * W * (4 + 4 + 2 + 2))
+        add("resid_norm_step (multiplier)", "resid_norm_step (channel scale, weight offset)", phase,
+            lambda: M.resid_norm_step(x32, y, None, None, wv, 1e-5, bf, 0.5), T * W * (4 + 4 + 2 + 2))
+        # latent attention: rotation with scaled frequencies and amplitude, causal attention, output gates
+        q = torch.randn(T, H * (d + rot), device=dev).to(bf)
+        q_abs = torch.randn(H, T, r, device=dev).to(bf).transpose(0, 1)
+        kvp = torch.randn(T, r + rot, device=dev).to(bf)
+        kn = torch.ones(r, device=dev, dtype=bf)
+        inv, amp = DSLatentSinkAttention.rotary_table(rot, 10000.0, RotaryScalingConfig(**PIFAZEN["yarn"]))
+        inv = inv.to(dev)
+        inv0 = DSLatentSinkAttention.rotary_table(rot, 10000.0)[0].to(dev)
+        cache = torch.randn(n_seq * n_pages_seq, 64, 1, r + rot, device=dev).to(bf)
+        prep_bytes = T * ((r + rot) * 4 + H * (r + rot) * (2 + 4))
+        add("latent_qk_prepare (scaled frequencies, amplitude)", None, phase,
+            lambda: M.latent_qk_prepare(q, q_abs, kvp, kn, inv, cache, t2s, pos, tables, H, d, rot, 1e-5, amp), prep_bytes)
+        add("latent_qk_prepare", "latent_qk_prepare (scaled frequencies, amplitude)", phase,
+            lambda: M.latent_qk_prepare(q, q_abs, kvp, kn, inv0, cache, t2s, pos, tables, H, d, rot, 1e-5), prep_bytes)
+        wrap = RaggedBatchWrapper(max(T, 64), n_seq, n_pages_seq, device=dev)
+
+        class _Seq:
+            def __init__(self, i):
+                self.seen_tokens, self._b = seen, tables[i].cpu()
+
+            def kv_blocks(self):
+                return self._b
+        for i in range(n_seq):
+            wrap.insert_sequence(_Seq(i), torch.zeros(per, dtype=torch.int32), do_checks=False)
+        wrap.finalize()
+        atoms, n_long = wrap.atoms(), wrap.atoms_longer_than(M.SHORT_ATOM)
+        sink = torch.zeros(H, device=dev)
+        ql = torch.randn(T, H, r + rot, device=dev)
+        keys_per_q = (per + 1) / 2 if phase == "prefill" else tot
+        att_bytes = n_seq * tot * (r + rot) * 2 + T * H * ((r + rot) * 4 + r * 2)
+        att_flops = 2.0 * T * H * (2 * r + rot) * keys_per_q
+        add("sink_attention, latent rows (causal, no sink)", None, phase,
+            lambda: M.sink_attention(ql, cache, None, None, t2s, pos, tables, 0.06, 0, bf, atoms, n_long, value_cols=r),
+            att_bytes, att_flops, "fp32")
+        add(f"sink_attention, latent rows (window {tot}, sink)", "sink_attention, latent rows (causal, no sink)", phase,
+            lambda: M.sink_attention(ql, cache, None, sink, t2s, pos, tables, 0.06, 0, bf, atoms, n_long, window=tot,
+                                     value_cols=r), att_bytes, att_flops, "fp32")
+        ctx = torch.randn(T, H * d, device=dev).to(bf)
+        gpc, gph = torch.randn(T, H * d, device=dev).to(bf), torch.randn(T, (H + 7) // 8 * 8, device=dev).to(bf)
+        add("sigmoid_gate_rows (per channel)", None, phase, lambda: M.sigmoid_gate_rows_(ctx, gpc, 1), T * H * d * 6)
+        add("sigmoid_gate_rows (per head)", None, phase, lambda: M.sigmoid_gate_rows_(ctx, gph[:, :H], d), T * H * d * 4)
+        acc, gl = torch.randn(T, H * d, device=dev).to(bf), torch.randn(T, device=dev)
+        add("row_gate_add", "sigmoid_gate_rows (per channel)", phase, lambda: M.row_gate_add_(acc, ctx, gl), T * H * d * 6)
+        # delta rule: decay per key channel beside one decay per head
+        a_raw, b_raw = torch.randn(T, H * d, device=dev).to(bf), torch.randn(T, (H + 7) // 8 * 8, device=dev).to(bf)
+        A_log, dtb, dtb1 = torch.zeros(H, device=dev), torch.zeros(H * d, device=dev), torch.zeros(H, device=dev)
+        add("channel_decay_gates", None, phase,
+            lambda: M.channel_decay_gates(a_raw, b_raw[:, :H], A_log, dtb, H, d), T * H * d * (2 + 4) + T * H * 6)
+        add("recurrence_gates", "channel_decay_gates", phase,
+            lambda: M.recurrence_gates(b_raw[:, :H], b_raw[:, :H], A_log, dtb1, "delta"), T * H * (2 * 2 + 2 * 4))
+        xs = torch.randn(T, 3 * H * d, device=dev)
+        xs[:, : 2 * H * d] /= math.sqrt(d)
+        decay_c = torch.rand(T, H * d, device=dev) * 0.1 + 0.9
+        decay_h, beta = torch.rand(T, H, device=dev) * 0.1 + 0.9, torch.rand(T, H, device=dev)
+        S0 = torch.zeros(n_seq, H, d, d, device=dev)
+        sb = (2 if seen else 1) * 4
+        rec_flops = 6.0 * T * H * d * d
+        add("linear_recurrence (delta, decay per key channel)", None, phase,
+            lambda: M.linear_recurrence(xs[:, H * d: 2 * H * d], xs[:, : H * d], xs[:, 2 * H * d:], decay_c, beta, None, S0,
+                                        info, H, H, d, d, True),
+            n_seq * H * d * d * sb + T * (4 * H * d * 4 + H * d * 4), rec_flops + 2.0 * T * H * d * d, "fp32")
+        add("linear_recurrence (delta, decay per head)", "linear_recurrence (delta, decay per key channel)", phase,
+            lambda: M.linear_recurrence(xs[:, H * d: 2 * H * d], xs[:, : H * d], xs[:, 2 * H * d:], decay_h, beta, None, S0,
+                                        info, H, H, d, d, True),
+            n_seq * H * d * d * sb + T * (3 * H * d * 4 + H * d * 4), rec_flops, "fp32")
+        o0 = torch.randn(T, H * d, device=dev)
+        gate = torch.randn(T, H * d, device=dev).to(bf)
+        nw = torch.ones(d, device=dev, dtype=bf)
+        add("group_norm_gate (sigmoid gate)", None, phase,
+            lambda: M.group_norm_gate(o0, gate, nw, d, 1e-5, False, bf, sigmoid=True), T * H * d * (4 + 2 + 2))
+        add("group_norm_gate (silu gate)", "group_norm_gate (sigmoid gate)", phase,
+            lambda: M.group_norm_gate(o0, gate, nw, d, 1e-5, False, bf), T * H * d * (4 + 2 + 2))
+        # feed-forwards
+        hu = torch.randn(T, ff, device=dev).to(bf)
+        bu = torch.zeros(ff, device=dev, dtype=bf)
+        coef = torch.tensor([0.6, 0.3, 0.2, 0.05], device=dev)
+        add("power_norm_act", None, phase, lambda: M.power_norm_act(hu, bu, coef, 1e-5), T * ff * 4)
+        add("bias_act_rows (squared relu)", "power_norm_act", phase, lambda: M.bias_act_rows(hu, bu, "relu_sq"), T * ff * 4)
+        E, n_id, K, Fe = PIFAZEN["experts"], PIFAZEN["identity"], PIFAZEN["top"], ff // 4
+        hg = torch.randn(T * K, 2 * Fe, device=dev).to(bf)
+        add("gated_act_rows (clamped)", None, phase, lambda: M.gated_act_rows(hg, "clamped_swish", 7.0), T * K * Fe * 6)
+        add("gated_act (silu)", "gated_act_rows (clamped)", phase, lambda: F.gated_act(hg, "silu"), T * K * Fe * 6)
+        logits = torch.randn(T, E + n_id, device=dev)
+        corr = torch.zeros(E + n_id, device=dev)
+        gate_bytes = T * ((E + n_id) * 4 + K * 12)
+        add("grouped_top_k_gating (correction, groups, scale)", None, phase,
+            lambda: moe_ops.top_k_gating(logits, K, correction=corr, n_groups=PIFAZEN["groups"],
+                                         keep_groups=PIFAZEN["keep"], scale=PIFAZEN["scale"]), gate_bytes)
+        add("top_k_gating (softmax)", "grouped_top_k_gating (correction, groups, scale)", phase,
+            lambda: moe_ops.top_k_gating(logits[:, :E].contiguous(), K, renormalize=True), T * (E * 4 + K * 12))
+        xe = torch.randn(T, W, device=dev).to(bf)
+        w1 = (torch.randn(E, 2 * Fe, W, device=dev) / math.sqrt(W)).to(bf)
+        w2 = (torch.randn(E, W, Fe, device=dev) / math.sqrt(Fe)).to(bf)
+        moe_bytes = E * 3 * Fe * W * 2 + T * W * 2 * (1 + 2 * K + 1) + T * K * 3 * Fe * 2
+        moe_flops = 2.0 * T * K * 3 * Fe * W
+
+        def experts(identity):
+            if identity:
+                s, a, o, c = moe_ops.top_k_gating(logits, K, correction=corr, n_groups=PIFAZEN["groups"],
+                                                  keep_groups=PIFAZEN["keep"], scale=PIFAZEN["scale"])
+                return fused_ep.grouped_experts_inference(xe, s, a, o, c, w1, w2,
+                                                          lambda t: M.gated_act_rows(t, "clamped_swish", 7.0), K,
+                                                          n_identity=n_id)
+            s, a, o, c = moe_ops.top_k_gating(logits[:, :E].contiguous(), K, renormalize=False)
+            return fused_ep.grouped_experts_inference(xe, s, a, o, c, w1, w2, F.swiglu, K)
+        add("experts: group-limited gating, clamped experts, identity rows copied", None, phase,
+            lambda: experts(True), moe_bytes, moe_flops, "bf16")
+        add("experts: softmax gating, rows in, grouped GEMMs, weighted sum", "experts: group-limited gating, clamped "
+            "experts, identity rows copied", phase, lambda: experts(False), moe_bytes, moe_flops, "bf16")
+    by_name = {(r_["kernel"], r_["phase"]): r_ for r_ in rows}
+    for r_ in rows:                      # distance from the roofline relative to the like kernel's
+        if r_["like"]:
+            mine = by_name[(r_["like"], r_["phase"])]
+            mine["like_of_roofline"] = r_["of_roofline"]
+            mine["like_kernel"] = r_["kernel"]
+    return rows
+
+
 def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, warmup: int, kernels: bool = True,
         chunk: int = 0, model: str = "fomalix") -> Dict:
     global CHUNK, WINDOW
@@ -733,6 +973,20 @@ def run(sizes: List[str], prefill: int, batch: int, context: int, steps: int, wa
                      "fomalix": engine_throughput(build_hybrid, z, prefill, batch, context, steps, warmup, timer)}
             if kernels:
                 entry["kernels"] = kekopel_kernel_table(z, prefill, batch, context, timer, hbm, peak_tflops)
+            out["sizes"][name] = entry
+        return out
+    if model == "pifazen":
+        out["metric"] = "serving tokens/s, Pifazen vs Kekopel stack of equal size"
+        out["pifazen"], out["latent"] = PIFAZEN, LATENT
+        WINDOW = CHUNK = max(WINDOW, prefill, context + steps + warmup + 8)    # the Kekopel window holds every key: equal work
+        out["attention_window"] = out["attention_chunk"] = WINDOW
+        for name in sizes:
+            z = SIZES[name]
+            entry = {"config": z,
+                     "pifazen": engine_throughput(build_pifazen, z, prefill, batch, context, steps, warmup, timer),
+                     "kekopel": engine_throughput(build_kekopel, z, prefill, batch, context, steps, warmup, timer)}
+            if kernels:
+                entry["kernels"] = pifazen_kernel_table(z, prefill, batch, context, timer, hbm, peak_tflops)
             out["sizes"][name] = entry
         return out
     if model == "ridazen":

@@ -2226,12 +2226,12 @@ power_norm_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, const
 }
 
 // The same with the row held in registers between the two passes: VEC channels per 16-byte access, up to CH accesses per
-// thread (F <= 256 * VEC * CH), the three sums reduced together.
-template <typename T, int VEC, int CH>
-__global__ void __launch_bounds__(256)
+// thread (F <= NT * VEC * CH, NT threads per CTA), the three sums reduced together.
+template <typename T, int VEC, int CH, int NT>
+__global__ void __launch_bounds__(NT)
 power_norm_act_vec_kernel(const T* __restrict__ x, const T* __restrict__ bias, const float* __restrict__ coef,
                           T* __restrict__ out, int F, float eps) {
-  __shared__ float red[3][8];
+  __shared__ float red[3][NT / 32];
   struct alignas(16) Pack { T v[VEC]; };
   const long long base = (long long)blockIdx.x * F;
   const int nvec = F / VEC;
@@ -2239,7 +2239,7 @@ power_norm_act_vec_kernel(const T* __restrict__ x, const T* __restrict__ bias, c
   float s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
   for (int k = 0; k < CH; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < nvec) {
       z[k] = *reinterpret_cast<const Pack*>(x + base + (long long)i * VEC);
       if (bias != nullptr) {
@@ -2260,12 +2260,12 @@ power_norm_act_vec_kernel(const T* __restrict__ x, const T* __restrict__ bias, c
   __syncthreads();
   s1 = s2 = s3 = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) s1 += red[0][i], s2 += red[1][i], s3 += red[2][i];
+  for (int i = 0; i < NT / 32; ++i) s1 += red[0][i], s2 += red[1][i], s3 += red[2][i];
   const float a = coef[0] / sqrtf(s1 / (float)F + eps), b = coef[1] / sqrtf(s2 / (float)F + eps),
               c3 = coef[2] / sqrtf(s3 / (float)F + eps), e = coef[3];
 #pragma unroll
   for (int k = 0; k < CH; ++k) {
-    const int i = threadIdx.x + k * 256;
+    const int i = threadIdx.x + k * NT;
     if (i < nvec) {
       Pack o;
 #pragma unroll
@@ -2375,19 +2375,19 @@ SXB_API int sxb_power_norm_act(const void* in, const void* bias, const void* coe
   if (aligned && F <= 256 * per * 8 && (dtype == 0 || dtype == 2)) {
     cudaStream_t s = (cudaStream_t)stream;
     const int chunks = (F / per + 255) / 256;
-#define POWER_NORM(CH)                                                                                              \
+#define POWER_NORM(CH, NT)                                                                                          \
   do {                                                                                                              \
     if (dtype == 0)                                                                                                 \
-      power_norm_act_vec_kernel<float, 4, CH><<<(unsigned)rows, 256, 0, s>>>(                                       \
+      power_norm_act_vec_kernel<float, 4, CH, NT><<<(unsigned)rows, NT, 0, s>>>(                                    \
           (const float*)in, (const float*)bias, (const float*)coef, (float*)out, F, eps);                           \
     else                                                                                                            \
-      power_norm_act_vec_kernel<__nv_bfloat16, 8, CH><<<(unsigned)rows, 256, 0, s>>>(                               \
+      power_norm_act_vec_kernel<__nv_bfloat16, 8, CH, NT><<<(unsigned)rows, NT, 0, s>>>(                            \
           (const __nv_bfloat16*)in, (const __nv_bfloat16*)bias, (const float*)coef, (__nv_bfloat16*)out, F, eps);   \
   } while (0)
-    if (chunks <= 1) POWER_NORM(1);
-    else if (chunks <= 2) POWER_NORM(2);
-    else if (chunks <= 4) POWER_NORM(4);
-    else POWER_NORM(8);
+    if (chunks <= 1) POWER_NORM(1, 256);
+    else if (chunks <= 2) POWER_NORM(2, 256);
+    else if (chunks <= 4) POWER_NORM(4, 256);
+    else POWER_NORM(4, 512);          // rows of up to 512 * 4 words: twice the threads instead of twice the registers
 #undef POWER_NORM
     SXB_CHECK_LAUNCH();
     return SXB_OK;

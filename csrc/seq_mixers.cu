@@ -20,6 +20,8 @@
 //                         x += scale (.) rms(y) * gain behind it (+ a weighted sum of all layers' streams), final norm
 //   rms_norm_slice, latent_qk_prepare   latent attention: query latent norm; key latent norm + rotation + cache append
 //   mlstm_prepare / mlstm_gate_scan / mlstm_output   matrix-memory LSTM around linear_recurrence
+//   channel_decay_gates   decay per head AND key channel for linear_recurrence (its per-channel form), sigmoid write strength
+//   sigmoid_gate_rows, power_norm_act   sigmoid gate per channel or per head in place; a z/rms(z) + b z^2/rms(z^2) + c z^3/rms(z^3) + e
 #include <algorithm>
 #include "sxb_common.cuh"
 #include <cuda_pipeline.h>

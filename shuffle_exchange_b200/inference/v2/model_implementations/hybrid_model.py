@@ -148,7 +148,11 @@ class DSHybridModel(DSInferenceModelBase):
     ``dt_bias``, ``D`` (fp32), ``norm``.  Pre-scaled stacks: one norm weight per sublayer (``norm1``, ``norm2``), attention
     with filtered projections ``conv_w``, ``q_norm``, ``k_norm``, ``dist_bias`` (fp32 ``[heads, distances]``); experts
     ``moe_gate`` (fp32, the shared expert's gate row last), ``moe_gate_b``, ``moe_w1``, ``moe_w2``, ``shared_up``,
-    ``shared_down``; token input ``side_gate``, ``side_proj``, ``side_norm`` and the global ``side_embed``."""
+    ``shared_down``; token input ``side_gate``, ``side_proj``, ``side_norm`` and the global ``side_embed``.  With
+    ``layer_scale``: ``ls1``, ``ls2``.  Channel delta rule: ``conv_w``, ``A_log``, ``dt_bias`` (fp32), ``w_a2``, ``w_g2``,
+    ``norm``; latent attention ``q_norm``, ``w_uq`` (not with direct queries), ``kv_norm``, ``w_uk``, ``w_uv_t``; three-power
+    feed-forward ``w_up``, ``b_up``, ``w_down``, ``b_down``, ``act_coef`` (fp32); group-limited experts ``moe_gate``,
+    ``moe_correction`` (fp32), ``moe_w1``, ``moe_w2``.  Two entries of ``layers`` may be one object (borrowed weights)."""
 
     def __init__(self, spec: HybridSpec, weights: Dict, engine_config: RaggedInferenceEngineConfig, state_manager=None,
                  base_mp_group=None) -> None:

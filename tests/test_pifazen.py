@@ -529,17 +529,12 @@ def test_greedy_generation_through_the_scheduler():
     assert eng.free_blocks == 40 and eng._state_manager.n_tracked_sequences == 0
 
 
-def test_command_line_generation_from_a_checkpoint_folder(tmp_path):
-    """``config.json`` + ``model.safetensors`` (bf16) on disk, ``bin/sxb_generate`` picks the model class by the
-    configuration, loads the tensors by their checkpoint names and continues two prompts greedily."""
+def write_checkpoint(folder, cfg, W):
+    """``config.json`` + ``model.safetensors`` (bf16): 8-byte header length, JSON header, tensor bytes."""
     import json
-    import os
     import struct
-    import subprocess
-    import sys
-    W = O.random_weights(STACK, seed=14)
-    with open(tmp_path / "config.json", "w") as f:
-        json.dump(STACK, f)
+    with open(folder / "config.json", "w") as f:
+        json.dump(cfg, f)
     meta, blobs, off = {}, [], 0
     for name, t in W.items():
         b = t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
@@ -547,8 +542,19 @@ def test_command_line_generation_from_a_checkpoint_folder(tmp_path):
         blobs.append(b)
         off += len(b)
     header = json.dumps(meta).encode()
-    with open(tmp_path / "model.safetensors", "wb") as f:
+    with open(folder / "model.safetensors", "wb") as f:
         f.write(struct.pack("<Q", len(header)) + header + b"".join(blobs))
+
+
+def test_command_line_generation_from_a_checkpoint_folder(tmp_path):
+    """``bin/sxb_generate`` picks the model class by the configuration, loads the tensors by their checkpoint names and
+    continues two prompts greedily."""
+    import json
+    import os
+    import subprocess
+    import sys
+    W = O.random_weights(STACK, seed=14)
+    write_checkpoint(tmp_path, STACK, W)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     prompts = [[5, 17, 3], [9, 9, 1, 2, 3, 4, 5, 6, 7]]
     cmd = [sys.executable, os.path.join(root, "bin", "sxb_generate"), "--model", str(tmp_path), "--max-new-tokens", "4",
@@ -562,3 +568,47 @@ def test_command_line_generation_from_a_checkpoint_folder(tmp_path):
     for p, x in zip(prompts, lines):
         _check_greedy(p, x["generated"], W, STACK)
         assert len(x["generated"]) == 4
+
+
+def test_replaying_a_schedule_of_steps_from_a_checkpoint_folder(tmp_path):
+    """``bin/trace_run``: five requests through a pool of four 64-token pages and four state slots -- portions beside single tokens, a
+    request left out of a step, requests that end and whose pages and slot the next one takes -- write the logits of the
+    wanted positions per step; every one must equal the plain evaluation of its request alone."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import numpy as np
+    W = O.random_weights(STACK, seed=15)
+    model = tmp_path / "model"
+    model.mkdir()
+    write_checkpoint(model, STACK, W)
+    reqs = {name: tokens(n, STACK["vocab"], 50 + n) for name, n in (("a", 40), ("b", 9), ("c", 23), ("d", 1), ("e", 30))}
+    plan = [({"a": 17, "b": 2}, []), ({"a": 3, "b": 7, "c": 5, "d": 1}, ["b", "d"]), ({"a": 1, "c": 2, "e": 11}, []),
+            ({"a": 19, "e": 1}, ["a"]), ({"c": 16, "e": 18}, ["c", "e"])]
+    at = {k: 0 for k in reqs}
+    steps, wanted = [], []
+    for i, (portion, end) in enumerate(plan):
+        entries = []
+        for name, n in portion.items():
+            want = sorted({0, n - 1, n // 2})
+            entries.append({"id": name, "tokens": reqs[name][at[name]: at[name] + n], "want": want})
+            wanted += [(i, name, at[name] + w) for w in want]
+            at[name] += n
+        steps.append(json.dumps({"step": i, "entries": entries, "end": end}))
+    assert at == {k: len(v) for k, v in reqs.items()}
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    cmd = [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model), "--dtype", "float32", "--out",
+           str(out), "--max-tokens", "256"] + ([] if torch.cuda.is_available() else ["--device", "cpu"])
+    r = subprocess.run(cmd, input="\n".join(steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [x for x in r.stdout.splitlines() if x.startswith("done")] == [f"done {i}" for i in range(len(plan))]
+    full = {name: O.forward(STACK, W, t) for name, t in reqs.items()}
+    got = {i: torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4").reshape(-1, STACK["vocab"])).double()
+           for i in range(len(plan))}
+    row = {i: 0 for i in got}
+    for i, name, p in wanted:
+        close(got[i][row[i]: row[i] + 1], full[name][p: p + 1])
+        row[i] += 1
+    assert all(row[i] == got[i].shape[0] for i in got)

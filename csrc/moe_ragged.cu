@@ -93,9 +93,9 @@ top_k_gating_kernel(const T* __restrict__ logits, float* __restrict__ scores, in
 }
 
 // Group-limited gating with a choice correction, one warp per token.  Scores are the softmax over all E router outputs
-// (fp32); the CHOICE is made by score + correction: the experts form n_groups equal groups of neighbours, a group's rank
+// (fp32); the CHOICE is made by score + correction: the experts form n_groups contiguous blocks of equal size, a group's rank
 // is the largest choice value in it, only members of the keep_groups best groups can win, and the top_k largest choice
-// values among them are taken.  The weights are the winners' plain scores (no correction), divided by their sum + 1e-20
+// values among them are taken.  The weights are the winners' plain scores (no correction), normalised by their total plus 1e-20
 // and multiplied by `scale`.  Outputs as top_k_gating_kernel.
 constexpr int kMaxGroups = 128;
 __global__ void __launch_bounds__(256)
@@ -573,7 +573,7 @@ SXB_API int sxb_top_k_gating(const void* logits, void* scores, void* assignments
 }
 
 // Group-limited gating with a choice correction.  logits fp32 [T, E]; correction fp32 [E] or null; the E experts form
-// n_groups equal groups of neighbours of which the keep_groups whose best (score + correction) is largest stay eligible;
+// n_groups contiguous blocks of equal size of which the keep_groups whose best (score + correction) is largest stay eligible;
 // the top_k largest (score + correction) among them win; scores fp32 [T, K] = softmax score of the winner / (sum of the
 // winners' scores + 1e-20) * scale; assignments / offsets / expert_counts as sxb_top_k_gating.
 SXB_API int sxb_grouped_top_k_gating(const void* logits, const void* correction, void* scores, void* assignments,

@@ -20,8 +20,8 @@
 //                         x += scale (.) rms(y) * gain behind it (+ a weighted sum of all layers' streams), final norm
 //   rms_norm_slice, latent_qk_prepare   latent attention: query latent norm; key latent norm + rotation + cache append
 //   mlstm_prepare / mlstm_gate_scan / mlstm_output   matrix-memory LSTM around linear_recurrence
-//   channel_decay_gates   decay per head AND key channel for linear_recurrence (its per-channel form), sigmoid write strength
-//   sigmoid_gate_rows, power_norm_act   sigmoid gate per channel or per head in place; a z/rms(z) + b z^2/rms(z^2) + c z^3/rms(z^3) + e
+//   channel_decay_gates   decay per (head, key channel) pair for linear_recurrence (its per-channel form), sigmoid write strength
+//   sigmoid_gate_rows, power_norm_act   sigmoid gate per channel or per head in place; p1 z/rms(z) + p2 z^2/rms(z^2) + p3 z^3/rms(z^3) + p0
 #include <algorithm>
 #include "sxb_common.cuh"
 #include <cuda_pipeline.h>
@@ -891,7 +891,7 @@ recurrence_gates_kernel(const T* __restrict__ a_raw, const T* __restrict__ b_raw
   beta[i] = mode == 0 ? sigmoid_f(to_f32<T>(b_raw[(long long)t * ld + h])) : dt;
 }
 
-// Decay per head AND key channel:  decay[t, h, c] = exp(-exp(A_log[h]) * softplus(a_raw[t, h n + c] + dt_bias[h n + c])),
+// Decay per (head, key channel) pair:  decay[t, h, c] = exp(-exp(A_log[h]) * softplus(a_raw[t, h n + c] + dt_bias[h n + c])),
 // beta[t, h] = sigmoid(b_raw[t, h]).  a_raw rows of pitch lda hold H n channels, b_raw rows of pitch ldb hold H.
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -1170,7 +1170,7 @@ gated_act_rows_kernel(const T* __restrict__ in, T* __restrict__ out, long long t
   const int c = (int)(i % F);
   float gte = to_f32<T>(in[r * 2 * F + c]), up = to_f32<T>(in[r * 2 * F + F + c]);
   float a;
-  if (act == 5) {          // clamped: g = min(gate, limit), u = clamp(up, -limit, limit); g sigmoid(1.702 g) (u + 1)
+  if (act == 5) {          // clamped: a = min(gate, L), b = max(-L, min(up, L)); a sigmoid(1.702 a) (1 + b)
     gte = fminf(gte, limit);
     up = fminf(fmaxf(up, -limit), limit) + 1.f;
     a = gte * sigmoid_f(1.702f * gte);
@@ -1886,8 +1886,7 @@ SXB_API int sxb_recurrence_gates(const void* a_raw, const void* b_raw, long long
   return SXB_OK;
 }
 
-/* decay_channels != 0: decay fp32 [rows, H * n] holds one factor per head and key channel (the rows of S that belong to
- * that channel are multiplied by it).
+/* decay_channels != 0: decay fp32 [rows, H * n] holds one factor per (head, key channel) pair (it scales the state entries of that key channel).
  * Per sequence and head, rows in order:  S <- decay S;  u = beta (v - [delta] S^T k);  S <- S + k u^T;
  * o = S^T q (+ skip[h] v).  kvec / qvec fp32 [rows, ldkq] hold G heads of n channels, val fp32 [rows, ldv] H heads of dv,
  * decay / beta fp32 [rows, H], state fp32 [slots, H, dv, n] (taken as zero when the sequence has seen no token), out fp32
@@ -1941,7 +1940,7 @@ SXB_API int sxb_group_norm_gate(const void* y, const void* gate, long long ldg, 
 }
 
 /* out [rows, F] = act(in[:, :F]) * in[:, F:] for rows of any width; act: 0 identity, 1 relu, 2 gelu (tanh form), 3 silu,
- * 5 clamped: g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(1.702 g) (u + 1). */
+ * 5 clamped: a = min(gate, L), b = max(-L, min(up, L)), out = a sigmoid(1.702 a) (1 + b). */
 SXB_API int sxb_gated_act_rows(const void* in, void* out, long long rows, int F, int act, int dtype, float limit,
                                void* stream) {
   const long long total = rows * F;
@@ -2200,8 +2199,8 @@ sigmoid_gate_rows_vec_kernel(T* __restrict__ x, const T* __restrict__ gate, long
 }
 
 // Three-power normalised activation, one CTA per row of F channels:
-//   z = x + bias;  out = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e,   rms(u) = sqrt(mean(u^2) + eps)
-// coef fp32 [4] = (a, b, c, e).  The three sums of squares (z^2, z^4, z^6) come from one pass in 32-bit.
+//   z = x + bias;  out = p1 z / rms(z) + p2 z^2 / rms(z^2) + p3 z^3 / rms(z^3) + p0,   rms(u) = sqrt(mean(u^2) + eps)
+// coef fp32 [4] = (p1, p2, p3, p0).  The three sums of squares (z^2, z^4, z^6) come from one pass in 32-bit.
 template <typename T>
 __global__ void __launch_bounds__(256)
 power_norm_act_kernel(const T* __restrict__ x, const T* __restrict__ bias, const float* __restrict__ coef,
@@ -2366,7 +2365,7 @@ SXB_API int sxb_sigmoid_gate_rows(void* x, const void* gate, long long ldg, long
   return SXB_OK;
 }
 
-/* out `dtype` [rows, F]: z = in + bias; a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e with (a, b, c, e) = coef
+/* out `dtype` [rows, F]: z = in + bias; p1 z / rms(z) + p2 z^2 / rms(z^2) + p3 z^3 / rms(z^3) + p0 with (p1, p2, p3, p0) = coef
  * fp32 [4] and rms over the row (eps inside the root); bias `dtype` [F] or null. */
 SXB_API int sxb_power_norm_act(const void* in, const void* bias, const void* coef, void* out, long long rows, int F,
                                float eps, int dtype, void* stream) {

@@ -538,7 +538,7 @@ int sxb_router_logits(const void* x, long long ld, const void* w, const void* bi
 
 /* ---- csrc/moe_ragged.cu */
 /* Group-limited gating with a choice correction.  logits fp32 [T, E]; correction fp32 [E] or null; the E experts form
- * n_groups equal groups of neighbours of which the keep_groups whose best (score + correction) is largest stay eligible;
+ * n_groups contiguous blocks of equal size of which the keep_groups whose best (score + correction) is largest stay eligible;
  * the top_k largest (score + correction) among them win; scores fp32 [T, K] = softmax score of the winner / (sum of the
  * winners' scores + 1e-20) * scale; assignments / offsets / expert_counts as sxb_top_k_gating. */
 int sxb_grouped_top_k_gating(const void* logits, const void* correction, void* scores, void* assignments,

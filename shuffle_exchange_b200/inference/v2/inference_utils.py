@@ -63,7 +63,7 @@ class ActivationType(IntEnum):
     SiGLU = 5
     IDENTITY = 6
     RELU_SQ = 7          # relu(x) ** 2
-    CLAMPED_SWIGLU = 8   # gated: g = min(gate, limit), u = clamp(up, -limit, limit); g * sigmoid(1.702 g) * (u + 1)
+    CLAMPED_SWIGLU = 8   # gated: a = min(gate, L), b = max(-L, min(up, L)); a * sigmoid(1.702 a) * (1 + b)
     InvalidType = -1
 
 

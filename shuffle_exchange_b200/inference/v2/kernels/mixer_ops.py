@@ -449,7 +449,7 @@ def group_norm_gate(y: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, group_
 
 def gated_act_rows(x: torch.Tensor, act: str = "gelu", limit: float = 0.0) -> torch.Tensor:
     """``act(x[:, :F]) * x[:, F:]`` for rows of any width, bf16 or fp32 (``gelu`` is the tanh form).  ``clamped_swish``:
-    ``g = min(x[:, :F], limit)``, ``u = clamp(x[:, F:], -limit, limit)``, result ``g * sigmoid(1.702 g) * (u + 1)``."""
+    ``a = min(x[:, :F], L)``, ``b = max(-L, min(x[:, F:], L))`` with ``L = limit``, result ``a * sigmoid(1.702 a) * (1 + b)``."""
     T, F2 = x.shape
     Fh = F2 // 2
     if x.is_cuda:
@@ -483,8 +483,8 @@ def bias_act_rows(x: torch.Tensor, bias: Optional[torch.Tensor], act: str) -> to
 
 
 def power_norm_act(x: torch.Tensor, bias: Optional[torch.Tensor], coef: torch.Tensor, eps: float) -> torch.Tensor:
-    """Three-power normalised activation of every row: ``z = x + bias``; ``a z / rms(z) + b z^2 / rms(z^2) + c z^3 /
-    rms(z^3) + e`` with ``(a, b, c, e) = coef`` (fp32 ``[4]``) and ``rms(u) = sqrt(mean(u^2) + eps)`` over the row; the
+    """Three-power normalised activation of every row: ``z = x + bias``; ``p1 z / rms(z) + p2 z^2 / rms(z^2) + p3 z^3 /
+    rms(z^3) + p0`` with ``(p1, p2, p3, p0) = coef`` (fp32 ``[4]``) and ``rms(u) = sqrt(mean(u^2) + eps)`` over the row; the
     sums are 32-bit, input and output share their dtype (bf16 or fp32)."""
     T, Fw = x.shape
     if x.is_cuda:

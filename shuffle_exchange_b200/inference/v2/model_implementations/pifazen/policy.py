@@ -2,21 +2,21 @@
 (``hybrid_model.py``, block form ``"pre_scaled"`` with ``layer_scale``): ``x += ls1 (.) mixer(n1(x))``, ``x += ls2 (.)
 ff(n2(x))`` where ``n(x) = x / rms(x) * (1 + w)`` (the norm weights are stored around zero).  ``config.json`` lists every
 layer with its token mixer, the mixer's sizes and its feed-forward; a layer with ``weights_of: j`` has no tensors of
-its own and runs with layer ``j``'s, on a cache or state of its own.  The embedding table is also the head.
+its own and runs with layer ``j``'s, on its own cache or state.  The embedding table is also the head.
 
-Mixers.  ``channel_delta``: gated delta rule with one decay per head and key channel (``channel_delta_mixer``): q | k | v
+Mixers.  ``channel_delta``: gated delta rule with a separate decay for every key channel of every head (``channel_delta_mixer``): q | k | v
 through a short causal convolution and SiLU, q and k unit vectors, write strength ``sigmoid(W_b h)``, decay
 ``exp(-exp(A_log) softplus(W_a2 W_a1 h + dt_bias))``, per-head RMS norm times ``sigmoid(W_g2 W_g1 h)``.
 ``latent_attention``: queries through a normalised latent, keys and values as up-projections of one normalised latent
-per token plus one rotated key part shared by the heads (interleaved pairs), causal softmax, one sigmoid gate per output
+per token plus a single rotated key slice that every head uses (interleaved pairs), causal softmax, one sigmoid gate per output
 channel.  ``latent_attention_2``: queries straight from the input, rotation frequencies slowed by wavelength
-(``rot.scaling``: factor, original, fast, slow) with scaled cos and sin, one sigmoid gate per head.
+(the four numbers under ``rot.scaling``) with scaled cos and sin, one sigmoid gate per head.
 
 Feed-forwards.  ``dense``: ``W_down act(W_up h + b) + b`` with the three-power normalised activation ``a N(z) + b N(z^2) +
-c N(z^3) + e``.  ``moe``: clamped gated experts without biases (``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``,
-``g sigmoid(1.702 g) (u + 1)``); softmax scores over ``experts + identity`` router outputs, the choice made by score +
-``correction`` inside the best ``groups.keep`` of ``groups.count`` groups of neighbours, weights = chosen scores / their
-sum * ``router.scale``; the last ``router.identity`` outputs are experts that return their input.
+c N(z^3) + e``.  ``moe``: clamped gated experts without biases (``a = min(gate, L)``, ``b = max(-L, min(up, L))``,
+``a sigmoid(1.702 a) (1 + b)``); softmax scores over ``experts + identity`` router outputs, the choice made by score +
+``correction`` inside the best ``groups.keep`` of ``groups.count`` contiguous blocks, weights = chosen scores / their
+sum, times the router's ``scale``; the router's trailing ``identity`` outputs stand for experts that hand their input on.
 
 Checkpoint names: ``embed``, ``final.norm``, and per layer ``l<i>.norm1|norm2|ls1|ls2``, ``l<i>.mix.*`` (channel_delta:
 ``q``, ``k``, ``v`` with ``.conv`` filters, ``b``, ``A_log``, ``a1``, ``a2``, ``dt_bias``, ``g1``, ``g2``, ``norm``, ``o``;

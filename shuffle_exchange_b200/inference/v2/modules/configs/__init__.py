@@ -32,7 +32,7 @@ class RotaryScalingConfig(DeepSpeedConfigModel):
     """Frequency interpolation by wavelength for contexts ``factor`` times longer than ``original`` positions: pairs
     that complete fewer than ``slow`` turns over the original context are slowed by ``factor``, pairs with more than
     ``fast`` turns keep their frequency, the ones between are blended along a linear ramp over the pair index; cos and
-    sin are multiplied by ``0.1 ln(factor) + 1``."""
+    sin carry the factor ``1 + 0.1 ln(factor)``."""
     factor: float
     original: float
     fast: float = 32.0

@@ -21,7 +21,7 @@
                               query temperature, learned distance-bucket bias on the scores, sigmoid output gate
  ``gated_delta_mixer`` / ``ssd_mixer``   short convolutions with carried inputs + linear recurrence with a matrix
                               state per (sequence slot, head) + gated group norm
- ``channel_delta_mixer``      the delta rule with one decay per head and key channel and a sigmoid output gate, both
+ ``channel_delta_mixer``      the delta rule with a separate decay for every key channel of every head and a sigmoid output gate, both
                               from two-step projections
 =========================  =======================================================================================
 """
@@ -579,7 +579,7 @@ class DSChannelDeltaMixer(_RecurrentMixer):
     """Gated delta rule whose decay differs per key channel.  Projection columns: ``q (G n) | k (G n) | v (H dv) | b (H,
     padded to a multiple of 8) | a (ra) | g (rg)``; q, k, v pass a short convolution + SiLU, q and k become unit vectors (q also times ``n^-1/2``),
     ``beta = sigmoid(b)``.  The decay comes from a two-step projection: ``decay[h, c] = exp(-exp(A_log[h]) softplus(
-    (w_a2 a)[h n + c] + dt_bias[h n + c]))``, one factor per head and key channel that multiplies the rows of the matrix
+    (w_a2 a)[h n + c] + dt_bias[h n + c]))``, one factor per (head, key channel) pair that multiplies the rows of the matrix
     memory belonging to that channel; then ``u = beta (v - S^T k); S <- S + k u^T; o = S^T q``.  The output is ``o /
     rms(o) * norm * sigmoid(w_g2 g)`` per head.  ``weights``: ``conv_w`` ``[2 G n + H dv, taps]``, ``A_log`` fp32 ``[H]``,
     ``dt_bias`` fp32 ``[H n]``, ``w_a2`` ``[H n, ra]``, ``w_g2`` ``[H dv, rg]``, ``norm`` ``[dv]``."""
@@ -760,8 +760,8 @@ class DSLatentSinkAttention(DSSelfAttentionBase):
         """fp32 angular frequencies ``base^(-2i / n_rot)`` of the ``n_rot / 2`` pairs and the factor on cos and sin.  With
         ``scaling``: let ``pair(t) = n_rot ln(original / (2 pi t)) / (2 ln base)`` be the (fractional) pair that makes
         ``t`` turns over the original context, ``lo = max(floor(pair(fast)), 0)``, ``hi = min(ceil(pair(slow)), n_rot - 1)``
-        and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``; pair ``i`` turns at ``f_i / factor * ramp_i + f_i *
-        (1 - ramp_i)`` and the amplitude is ``0.1 ln(factor) + 1``.  Evaluated in float64, stored as float32."""
+        and ``w_i = min(1, max(0, (i - lo) / max(hi - lo, 0.001)))``; pair ``i`` turns at ``f_i (1 - w_i) + w_i f_i /
+        factor`` and the amplitude is ``0.1 ln(factor) + 1``.  Evaluated in float64, stored as float32."""
         i = torch.arange(0, n_rot, 2, dtype=torch.float64) / 2.0
         f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / max(n_rot, 1))
         amp = 1.0

@@ -35,8 +35,8 @@ def top_k_gating(logits: torch.Tensor, top_k: int, renormalize: bool = True, sco
 
     Group-limited choice (softmax scores only; taken when ``correction`` is given, ``n_groups > 1`` or ``scale != 1``):
     the winners are the ``top_k`` largest ``score + correction`` (``correction`` fp32 ``[E]``) among the experts of the
-    ``keep_groups`` groups -- of ``n_groups`` equal groups of neighbouring experts -- whose best ``score + correction``
-    is largest; the returned scores are the winners' plain scores divided by their sum (+ 1e-20), times ``scale``.
+    ``keep_groups`` groups -- of ``n_groups`` equal contiguous blocks of experts -- whose best ``score + correction``
+    is largest; the returned scores are the winners' plain scores normalised by their total (1e-20 added), times ``scale``.
 
     ``offsets[t,k]`` is the arrival index of token ``t`` inside expert ``assignments[t,k]`` (a permutation of
     ``range(counts[e])`` per expert; on CUDA the order is nondeterministic, on CPU it is token order)."""

@@ -92,7 +92,7 @@ def rotate_pairs(x: torch.Tensor, freqs: List[float], amp: float) -> torch.Tenso
 
 # ------------------------------------------------------------------------------------------------ mixers
 def latent_attention(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict, eps: float, direct_query: bool) -> torch.Tensor:
-    """Keys and values as up-projections of one normalised latent per token, one rotated key part shared by the heads.
+    """Keys and values as up-projections of one normalised latent per token, a single rotated key slice that every head uses.
     ``direct_query``: queries straight from the input and one gate per head; else queries through a normalised latent
     and one gate per output channel."""
     T = h.shape[0]
@@ -130,7 +130,7 @@ def unit_vectors(x: torch.Tensor) -> torch.Tensor:
 
 def channel_delta(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict, eps: float,
                   state: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Gated delta rule with one decay per head and key channel.  Matrix memory ``S`` [key channel, value channel] per
+    """Gated delta rule with a separate decay for every key channel of every head.  Matrix memory ``S`` [key channel, value channel] per
     head: ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``."""
     T = h.shape[0]
     H, G, n, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
@@ -159,7 +159,7 @@ def channel_delta(h: torch.Tensor, P: Dict[str, torch.Tensor], m: Dict, eps: flo
 
 # ------------------------------------------------------------------------------------------------ feed-forwards
 def three_power_norm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
-    """``a N(z) + b N(z^2) + c N(z^3) + e`` with ``N`` dividing a row by its root mean square."""
+    """``p1 R(z) + p2 R(z^2) + p3 R(z^3) + p0`` with ``R(u) = u / rms(u)`` over a row and ``coef = (p1, p2, p3, p0)``."""
     return (coef[0] * rms_norm(z, None, eps) + coef[1] * rms_norm(z * z, None, eps)
             + coef[2] * rms_norm(z * z * z, None, eps) + coef[3])
 
@@ -177,7 +177,7 @@ def clamped_expert(h: torch.Tensor, gate_w, up_w, down_w, limit: float) -> torch
 
 def route(z: torch.Tensor, correction: torch.Tensor, top: int, n_groups: int, keep: int, scale: float):
     """``z`` [T, R] router outputs -> (chosen [T, top], weights [T, top]).  Choice by ``softmax(z) + correction`` inside
-    the ``keep`` groups of neighbours whose best member scores highest; weights from the softmax alone."""
+    the ``keep`` contiguous blocks whose best member scores highest; weights from the softmax alone."""
     T, R = z.shape
     s = torch.softmax(z, dim=-1)
     choice = s + correction
